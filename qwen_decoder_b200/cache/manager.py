@@ -1,7 +1,9 @@
 """The cache manager: what each run of a layer caches, grouped by need, in pages.
 
 A mixer declares its need: ``PagedKV`` (keys and values per token, all of them or a
-window), ``PagedRows`` (one row per token) or ``FixedState`` (a per-request tensor of fixed size), or nothing.  Runs
+window), ``PagedRows`` (one row per token) or ``FixedState`` (a per-request tensor of fixed size), or nothing;
+a run of a layer that needs both pages and a per-request state (a short convolution's kept inputs beside
+the keys and values) declares a tuple of one paged need and one ``FixedState``.  Runs
 with equal paged needs form a *group*: one page id serves every layer of the group
 (as one page serves all layers in the reference, kv_cache.h:16-29), and every group
 has pages and block tables of its own, so that a windowed group can give pages back
@@ -84,7 +86,8 @@ class CacheLayout:
 
     @classmethod
     def from_needs(cls, needs: Sequence[Optional[object]], cache_of: Sequence[Optional[int]]) -> "CacheLayout":
-        """``needs[e]``: the need of schedule entry e's mixer; ``cache_of[e]``: None or an earlier entry."""
+        """``needs[e]``: the need of schedule entry e (one need, a tuple of a paged need and a ``FixedState``, or
+        None); ``cache_of[e]``: None or an earlier entry."""
         groups: List[CacheGroup] = []
         paged: Dict[int, Tuple[int, int]] = {}
         fixed: Dict[int, int] = {}
@@ -106,19 +109,24 @@ class CacheLayout:
             owners[e] = e
             if need is None:
                 continue
-            if isinstance(need, PAGED_NEEDS):
-                g = by_need.get(need)
-                if g is None:
-                    g = len(groups)
-                    by_need[need] = g
-                    groups.append(CacheGroup(need))
-                paged[e] = (g, len(groups[g].entries))
-                groups[g].entries.append(e)
-            elif isinstance(need, FixedState):
-                fixed[e] = len(fixed_needs)
-                fixed_needs.append(need)
-            else:
-                raise TypeError(f"schedule entry {e}: unknown cache need {need!r}")
+            for part in (need if isinstance(need, tuple) else (need,)):
+                if isinstance(part, PAGED_NEEDS):
+                    if e in paged:
+                        raise TypeError(f"schedule entry {e}: more than one paged need")
+                    g = by_need.get(part)
+                    if g is None:
+                        g = len(groups)
+                        by_need[part] = g
+                        groups.append(CacheGroup(part))
+                    paged[e] = (g, len(groups[g].entries))
+                    groups[g].entries.append(e)
+                elif isinstance(part, FixedState):
+                    if e in fixed:
+                        raise TypeError(f"schedule entry {e}: more than one fixed-size state")
+                    fixed[e] = len(fixed_needs)
+                    fixed_needs.append(part)
+                else:
+                    raise TypeError(f"schedule entry {e}: unknown cache need {part!r}")
         return cls(groups, paged, fixed, fixed_needs, owners)
 
 

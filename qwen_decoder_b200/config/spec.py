@@ -24,11 +24,12 @@ class LayerSpec:
     ``prefix`` is the weight-name prefix of the layer (``model.layers.3.``).
     ``norms`` maps the block's norm roles to part specs (for the pre-norm block:
     ``input`` and ``post_mixer``).  ``feed_forward`` may be None where a block allows a layer
-    without one.  ``block_params``: further sizes and constants of the block itself.
+    without one, and so may ``mixer`` for a block that only works on the residual sum.  ``block_params``: further
+    sizes and constants of the block itself.
     """
     prefix: str
     block: str
-    mixer: PartSpec
+    mixer: Optional[PartSpec]
     feed_forward: Optional[PartSpec]
     norms: Dict[str, PartSpec]
     block_params: Dict[str, Any] = field(default_factory=dict)
@@ -41,10 +42,12 @@ class ScheduleEntry:
     ``layer`` indexes ``ModelSpec.layers`` (a layer may be named more than once).
     ``cache_of`` names the schedule entry whose cache this run uses: ``None`` means
     its own (the run writes what its mixer caches); an integer ``j < i`` means "read
-    what entry ``j`` cached", without writing.
+    what entry ``j`` cached", without writing.  ``visit``: which run of a repeated stretch this is (0, 1, ...),
+    for blocks that do something else on every pass.
     """
     layer: int
     cache_of: Optional[int] = None
+    visit: int = 0
 
 
 @dataclass(frozen=True)

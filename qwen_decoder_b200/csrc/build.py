@@ -47,11 +47,15 @@ LIBRARIES: Dict[str, str] = {
     "moe": "moe.cu",
     "norm_act": "norm_act.cu",
     "attention_sink": "attention_sink.cu",
+    "gated_block": "gated_block.cu",
+    "attention_diff": "attention_diff.cu",
 }
 HEADERS = ["common.cuh", "entry_points.h"]
 # further files a library's source includes (hashed into its key)
 EXTRA_DEPS: Dict[str, List[str]] = {
     "decode_attention_noalloc": ["attention_flash.cu", "decode_attention_noalloc.h"],
+    "gated_block": ["short_conv.cuh"],
+    "attention_diff": ["short_conv.cuh"],
 }
 
 _loaded: Dict[str, ctypes.CDLL] = {}

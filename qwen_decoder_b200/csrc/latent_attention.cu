@@ -38,8 +38,9 @@ template <> struct Vec16<bf16> {
 #define LA_TT 8             // tokens per CTA in absorb and expand
 
 // ----------------------------------------------------------------------------- prep
-// u row t (float32, stride ldu): columns [q_off, q_off + q_rank) the raw query latent, [kv_off, kv_off + r + dr)
-// the raw key/value latent followed by the key part that is rotated.
+// u row t (float32, stride ldu): columns [q_off, q_off + q_rank) the raw query latent (q_rank 0: the design has
+// none, its queries are a projection of the input itself), [kv_off, kv_off + r + dr) the raw key/value latent
+// followed by the key part that is rotated (dr 0: no such part).
 template <typename TC>
 __global__ void __launch_bounds__(256)
 latent_prep_kernel(const float* __restrict__ u, long long ldu, int q_off, int q_rank, int kv_off, int r, int dr,
@@ -57,7 +58,7 @@ latent_prep_kernel(const float* __restrict__ u, long long ldu, int q_off, int q_
   for (int i = threadIdx.x; i < r; i += blockDim.x) { float v = row[kv_off + i]; sk = fmaf(v, v, sk); }
   sq = block_sum(sq, scratch);
   sk = block_sum(sk, scratch);
-  const float iq = 1.0f / sqrtf(sq / (float)q_rank + eps);
+  const float iq = q_rank > 0 ? 1.0f / sqrtf(sq / (float)q_rank + eps) : 0.f;      // no query latent: nothing to norm
   const float ik = 1.0f / sqrtf(sk / (float)r + eps);
   for (int i = threadIdx.x; i < q_rank; i += blockDim.x)
     cq[(size_t)t * q_rank + i] = from_float<TC>(row[q_off + i] * iq * wq_norm[i]);
@@ -76,18 +77,20 @@ latent_prep_kernel(const float* __restrict__ u, long long ldu, int q_off, int q_
 }
 
 // ----------------------------------------------------------------------------- absorb
-// q [T, H * (dn + dr)] float32; Wuk [H * dn, r]; qcat [T, H, r + dr] float32.
+// q [T, H * (dn + dr)] float32, rows ldq apart; Wuk [H * dn, r]; qcat [T, H, r + dr] float32.
 template <typename TW>
 __global__ void __launch_bounds__(256)
-latent_absorb_kernel(const float* __restrict__ q, const TW* __restrict__ wuk, float* __restrict__ qcat, int T, int H,
-                     int dn, int dr, int r, const float* __restrict__ cos_t, const float* __restrict__ sin_t,
-                     int rot_dims, const int* __restrict__ positions, const float* __restrict__ pre) {
+latent_absorb_kernel(const float* __restrict__ q, long long ldq, const TW* __restrict__ wuk, float* __restrict__ qcat,
+                     int T, int H, int dn, int dr, int r, const float* __restrict__ cos_t,
+                     const float* __restrict__ sin_t, int rot_dims, const int* __restrict__ positions,
+                     const float* __restrict__ pre) {
   pdl_launch_dependents();
   pdl_wait();
   extern __shared__ float qs[];                // [LA_TT][dn]
   const int h = blockIdx.y, t0 = blockIdx.x * LA_TT;
   const int nt = min(LA_TT, T - t0);
-  const int W = r + dr, qw = H * (dn + dr);
+  const int W = r + dr;
+  const size_t qw = (size_t)ldq;              // q's rows are ldq floats apart (a column range of a wider buffer is fine)
   for (int i = threadIdx.x; i < LA_TT * dn; i += blockDim.x) {
     int tt = i / dn, d = i - tt * dn;
     qs[i] = tt < nt ? q[(size_t)(t0 + tt) * qw + (size_t)h * (dn + dr) + d] : 0.f;
@@ -135,9 +138,10 @@ latent_absorb_kernel(const float* __restrict__ q, const TW* __restrict__ wuk, fl
 // partial sums meet in shared memory.  grid (token tiles, heads).
 template <typename TW>
 __global__ void __launch_bounds__(256)
-latent_absorb_vec_kernel(const float* __restrict__ q, const TW* __restrict__ wuk, float* __restrict__ qcat, int T, int H,
-                         int dn, int dr, int r, const float* __restrict__ cos_t, const float* __restrict__ sin_t,
-                         int rot_dims, const int* __restrict__ positions) {
+latent_absorb_vec_kernel(const float* __restrict__ q, long long ldq, const TW* __restrict__ wuk,
+                         float* __restrict__ qcat, int T, int H, int dn, int dr, int r,
+                         const float* __restrict__ cos_t, const float* __restrict__ sin_t, int rot_dims,
+                         const int* __restrict__ positions) {
   pdl_launch_dependents();
   pdl_wait();
   constexpr int V = Vec16<TW>::N;
@@ -146,7 +150,8 @@ latent_absorb_vec_kernel(const float* __restrict__ q, const TW* __restrict__ wuk
   float* red = sm + LA_TT * dn;                // [LA_TT][r]
   const int h = blockIdx.y, t0 = blockIdx.x * LA_TT;
   const int nt = min(LA_TT, T - t0);
-  const int W = r + dr, qw = H * (dn + dr);
+  const int W = r + dr;
+  const size_t qw = (size_t)ldq;              // q's rows are ldq floats apart (a column range of a wider buffer is fine)
   for (int i = threadIdx.x; i < LA_TT * dn; i += blockDim.x) {
     int tt = i / dn, d = i - tt * dn;
     qs[i] = tt < nt ? q[(size_t)(t0 + tt) * qw + (size_t)h * (dn + dr) + d] : 0.f;
@@ -614,7 +619,7 @@ extern "C" int qd_latent_prep(const float* u, long long ldu, int q_off, int q_ra
                               const float* sin_t, int rot_dims, const int* positions, const int* slot_map, void* cq,
                               void* cache, int dtype, int write_cache, int T, cudaStream_t stream) {
   if (T <= 0) return 0;
-  if (rot_dims % 2 || rot_dims > dr || q_rank <= 0 || r <= 0) return QD_ERR_UNSUPPORTED;
+  if (rot_dims % 2 || rot_dims > dr || q_rank < 0 || r <= 0) return QD_ERR_UNSUPPORTED;
   if (dtype == QD_F32)
     qd_launch(latent_prep_kernel<float>, dim3(T), dim3(256), 0, stream, u, ldu, q_off, q_rank, kv_off, r, dr, wq_norm,
               wkv_norm, eps, cos_t, sin_t, rot_dims, positions, slot_map, (float*)cq, (float*)cache, write_cache);
@@ -628,7 +633,7 @@ extern "C" int qd_latent_prep(const float* u, long long ldu, int q_off, int q_ra
 
 // ``pre`` (float32 [H, T, r], or null): Wuk_h^T q_h already made by a batched library product; the kernel then only
 // lays it beside the rotated part.
-extern "C" int qd_latent_absorb(const float* q, const void* wuk, int w_dtype, float* qcat, int T, int H, int dn, int dr,
+extern "C" int qd_latent_absorb(const float* q, long long ldq, const void* wuk, int w_dtype, float* qcat, int T, int H, int dn, int dr,
                                 int r, const float* cos_t, const float* sin_t, int rot_dims, const int* positions,
                                 const float* pre, cudaStream_t stream) {
   if (T <= 0) return 0;
@@ -641,20 +646,20 @@ extern "C" int qd_latent_absorb(const float* q, const void* wuk, int w_dtype, fl
         !((uintptr_t)wuk & 15) && vsm <= 48 * 1024) {
       dim3 vgrid((T + LA_TT - 1) / LA_TT, H);
       if (w_dtype == QD_F32)
-        qd_launch(latent_absorb_vec_kernel<float>, vgrid, dim3(256), vsm, stream, q, (const float*)wuk, qcat, T, H, dn, dr,
+        qd_launch(latent_absorb_vec_kernel<float>, vgrid, dim3(256), vsm, stream, q, ldq, (const float*)wuk, qcat, T, H, dn, dr,
                   r, cos_t, sin_t, rot_dims, positions);
       else
-        qd_launch(latent_absorb_vec_kernel<bf16>, vgrid, dim3(256), vsm, stream, q, (const bf16*)wuk, qcat, T, H, dn, dr,
+        qd_launch(latent_absorb_vec_kernel<bf16>, vgrid, dim3(256), vsm, stream, q, ldq, (const bf16*)wuk, qcat, T, H, dn, dr,
                   r, cos_t, sin_t, rot_dims, positions);
       return qd_last_error();
     }
   }
   dim3 grid((T + LA_TT - 1) / LA_TT, H, (r + 255) / 256);
   if (w_dtype == QD_F32)
-    qd_launch(latent_absorb_kernel<float>, grid, dim3(256), smem, stream, q, (const float*)wuk, qcat, T, H, dn, dr, r,
+    qd_launch(latent_absorb_kernel<float>, grid, dim3(256), smem, stream, q, ldq, (const float*)wuk, qcat, T, H, dn, dr, r,
               cos_t, sin_t, rot_dims, positions, pre);
   else if (w_dtype == QD_BF16)
-    qd_launch(latent_absorb_kernel<bf16>, grid, dim3(256), smem, stream, q, (const bf16*)wuk, qcat, T, H, dn, dr, r,
+    qd_launch(latent_absorb_kernel<bf16>, grid, dim3(256), smem, stream, q, ldq, (const bf16*)wuk, qcat, T, H, dn, dr, r,
               cos_t, sin_t, rot_dims, positions, pre);
   else
     return QD_ERR_UNSUPPORTED;

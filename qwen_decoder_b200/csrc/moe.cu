@@ -12,7 +12,10 @@
 // score + a per-output correction and weigh by the plain score (``route_mode`` 1); the last outputs of the router
 // may be identity experts, which have no weights and whose output is the token's input itself (they get no row
 // tiles; combine adds weight * input); the gated activation may be the clamped form
-// min(g, L) * sigmoid(a * min(g, L)) * (clamp(u, -L, L) + 1) (``act`` 1) instead of silu(g) * u.
+// min(g, L) * sigmoid(a * min(g, L)) * (clamp(u, -L, L) + 1) (``act`` 1) instead of silu(g) * u.  ``route_mode`` 2 chooses
+// the ``top`` largest logits and weighs each by its own sigmoid, not renormalised.  A pair's weight may multiply the
+// expert's INPUT instead of its output (``in_scale`` of the gated product: W (w h) = w (W h), so both sums of the pair
+// are multiplied by w before the gate; combine then adds the pairs' outputs as they are).
 //
 // Nothing comes back to the host between these: counts, places and tiles stay on the device, so a step with
 // routed experts is captured in a CUDA graph like any other.  The products run on float32 FMA with the
@@ -100,7 +103,8 @@ moe_logits_kernel(const T* __restrict__ h, const T* __restrict__ wr, const float
 
 // One thread per token.  mode 0: the ``top`` largest logits (the lower index wins a tie) and the softmax over them.
 // mode 1: scores = softmax over all E logits; the ``top`` largest of score + corr[e] are chosen (the lower index wins
-// a tie); the weights are the chosen outputs' plain scores, not renormalised.
+// a tie); the weights are the chosen outputs' plain scores, not renormalised.  mode 2: the ``top`` largest logits, each
+// weighed by sigmoid(logit).
 __global__ void __launch_bounds__(128)
 moe_topk_kernel(float* __restrict__ logits, int n_tokens, int E, int top, int mode, const float* __restrict__ corr,
                 int* __restrict__ idx, float* __restrict__ wt) {
@@ -141,6 +145,10 @@ moe_topk_kernel(float* __restrict__ logits, int n_tokens, int E, int top, int mo
     idx[(size_t)t * top + k] = best;
     v[k] = bv;
     my[best] = -INFINITY;
+  }
+  if (mode == 2) {                                // each chosen output's own sigmoid
+    for (int k = 0; k < top; k++) wt[(size_t)t * top + k] = 1.0f / (1.0f + expf(-v[k]));
+    return;
   }
   float sum = 0.f;
   const float vmax = v[0];                        // the first chosen is the largest
@@ -203,15 +211,16 @@ moe_topk_warp_kernel(const float* __restrict__ logits, int n_tokens, int E, int 
     for (int j = 0; j < MT_PER_LANE; j++)
       if (lane + 32 * j == be) c[j] = -INFINITY;
     if (k == 0) first = bz;
-    const float w = mode == 1 ? bz : expf(bz - first);          // mode 0: the first chosen is the largest logit
+    // mode 0: the first chosen is the largest logit; mode 2: the chosen logit's own sigmoid
+    const float w = mode == 1 ? bz : mode == 2 ? 1.0f / (1.0f + expf(-bz)) : expf(bz - first);
     sum += w;
     if (lane == (k & 31)) {
       idx[(size_t)t * top + k] = be;
-      if (mode == 1) wt[(size_t)t * top + k] = w;
+      if (mode != 0) wt[(size_t)t * top + k] = w;
       else chosen = w;                          // top <= 32: one round per lane
     }
   }
-  if (mode != 1 && lane < top) wt[(size_t)t * top + lane] = chosen / sum;
+  if (mode == 0 && lane < top) wt[(size_t)t * top + lane] = chosen / sum;
 }
 
 // ----------------------------------------------------------------------------- sort
@@ -259,7 +268,7 @@ template <typename TI, typename TW, typename TO, int TM, bool GATED>
 __global__ void __launch_bounds__(256)
 moe_gemm_kernel(const TI* __restrict__ A, long long lda, const int* __restrict__ pair_at, int top, int by_token,
                 const TW* __restrict__ W1, const TW* __restrict__ W2, TO* __restrict__ out, int N, int K,
-                const int* __restrict__ meta, int E, MoeAct act) {
+                const int* __restrict__ meta, int E, MoeAct act, const float* __restrict__ in_scale) {
   pdl_launch_dependents();
   pdl_wait();
   const int n_tiles = meta[E + 1];
@@ -320,8 +329,9 @@ moe_gemm_kernel(const TI* __restrict__ A, long long lda, const int* __restrict__
     for (int j = 0; j < 4; j++) {
       int gn = n0 + tx * 4 + j;
       if (gn >= N) continue;
-      float v = acc1[i][j];
-      if (GATED) v = moe_gated(v, acc2[i][j], act);
+      const float sc = in_scale ? in_scale[pair_at[row0 + r]] : 1.0f;
+      float v = acc1[i][j] * sc;
+      if (GATED) v = moe_gated(v, acc2[i][j] * sc, act);
       out[(size_t)(row0 + r) * N + gn] = from_float<TO>(v);
     }
   }
@@ -336,7 +346,7 @@ template <typename TI, typename TW, typename TO, bool GATED>
 __global__ void __launch_bounds__(256)
 moe_gemv_kernel(const TI* __restrict__ A, long long lda, const int* __restrict__ pair_at, int top, int by_token,
                 const TW* __restrict__ W1, const TW* __restrict__ W2, TO* __restrict__ out, int N, int K,
-                const int* __restrict__ meta, int E, MoeAct act) {
+                const int* __restrict__ meta, int E, MoeAct act, const float* __restrict__ in_scale) {
   pdl_launch_dependents();
   pdl_wait();
   if ((int)blockIdx.y >= meta[E + 1]) return;
@@ -389,8 +399,9 @@ moe_gemv_kernel(const TI* __restrict__ A, long long lda, const int* __restrict__
 #pragma unroll
       for (int r = 0; r < MG_ROWS; r++) {
         if (r < rows) {
-          float v = warp_sum(a1[u][r]);
-          if (GATED) v = moe_gated(v, warp_sum(a2[u][r]), act);
+          const float sc = in_scale ? in_scale[pair_at[row0 + r]] : 1.0f;
+          float v = warp_sum(a1[u][r]) * sc;
+          if (GATED) v = moe_gated(v, warp_sum(a2[u][r]) * sc, act);
           if (lane == 0) out[(size_t)(row0 + r) * N + n + u] = from_float<TO>(v);
         }
       }
@@ -426,7 +437,7 @@ template <typename TO, bool GATED>
 __global__ void __launch_bounds__(128)
 moe_gemm_mma_kernel(const bf16* __restrict__ A, long long lda, const int* __restrict__ pair_at, int top, int by_token,
                     const bf16* __restrict__ W1, const bf16* __restrict__ W2, TO* __restrict__ out, int N, int K,
-                    const int* __restrict__ meta, int E, MoeAct act) {
+                    const int* __restrict__ meta, int E, MoeAct act, const float* __restrict__ in_scale) {
   pdl_launch_dependents();
   pdl_wait();
   if ((int)blockIdx.y >= meta[E + 1]) return;
@@ -499,8 +510,9 @@ moe_gemm_mma_kernel(const bf16* __restrict__ A, long long lda, const int* __rest
     for (int q = 0; q < 4; q++) {
       int r = warp * 16 + g + (q >> 1) * 8, n = n0 + j * 8 + 2 * tq + (q & 1);
       if (r < rows && n < N) {
-        float v = c1[j][q];
-        if (GATED) v = moe_gated(v, c2[j][q], act);
+        const float sc = in_scale ? in_scale[pair_at[row0 + r]] : 1.0f;
+        float v = c1[j][q] * sc;
+        if (GATED) v = moe_gated(v, c2[j][q] * sc, act);
         out[(size_t)(row0 + r) * N + n] = from_float<TO>(v);
       }
     }
@@ -523,7 +535,7 @@ moe_combine_kernel(const float* __restrict__ y, const int* __restrict__ place, c
   if (threadIdx.x < top) {
     const size_t p = (size_t)t * top + threadIdx.x;
     s_row[threadIdx.x] = (idx && idx[p] >= E_real) ? -1 : place[p];
-    s_wt[threadIdx.x] = wt[p];
+    s_wt[threadIdx.x] = wt ? wt[p] : 1.0f;          // no weights: the pairs' outputs are added as they are
   }
   __syncthreads();
   const float sg = (shared && sgate) ? sgate[t] : 1.0f;
@@ -588,11 +600,12 @@ extern "C" int qd_moe_sort(const int* idx, int n_pairs, int E, int E_real, int t
   return qd_last_error();
 }
 
-// gated != 0: out[place, N] = silu(A W1_e^T) * (A W2_e^T) in ``out_dtype``; else out = A W1_e^T.
+// gated != 0: out[place, N] = silu(A W1_e^T) * (A W2_e^T) in ``out_dtype``; else out = A W1_e^T.  in_scale (float32, one
+// per pair, or null): the sums of pair p are multiplied by in_scale[p] before the gate.
 extern "C" int qd_moe_gemm(const void* A, long long lda, int a_dtype, const int* pair_at, int top, int by_token,
                            const void* W1, const void* W2, int w_dtype, void* out, int out_dtype, int N, int K,
                            const int* meta, int E, int tile_rows, int max_tiles, int gated, int act_kind, float act_limit,
-                           float act_alpha, cudaStream_t stream) {
+                           float act_alpha, const float* in_scale, cudaStream_t stream) {
   const MoeAct act = {act_kind, act_limit, act_alpha};
   if (max_tiles <= 0) return 0;
   if (max_tiles > 65535 || (tile_rows != 8 && tile_rows != 16 && tile_rows != 64)) return QD_ERR_UNSUPPORTED;
@@ -608,7 +621,7 @@ extern "C" int qd_moe_gemm(const void* A, long long lda, int a_dtype, const int*
     if (smem > 48 * 1024)                                                                                            \
       cudaFuncSetAttribute(moe_gemv_kernel<TI, TW, TO, G>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);  \
     qd_launch(moe_gemv_kernel<TI, TW, TO, G>, grid, dim3(256), smem, stream, (const TI*)A, lda, pair_at, top, by_token, \
-              (const TW*)W1, (const TW*)W2, (TO*)out, N, K, meta, E, act);                                                \
+              (const TW*)W1, (const TW*)W2, (TO*)out, N, K, meta, E, act, in_scale);                                      \
   } while (0)
 #define MG_PICK(TI, TW, TO) do { if (gated) MG_GO(TI, TW, TO, true); else MG_GO(TI, TW, TO, false); } while (0)
     if (a_dtype == QD_F32 && w_dtype == QD_F32 && out_dtype == QD_F32) MG_PICK(float, float, float);
@@ -630,7 +643,7 @@ extern "C" int qd_moe_gemm(const void* A, long long lda, int a_dtype, const int*
       raised = true;                                                                                              \
     }                                                                                                             \
     qd_launch(moe_gemm_mma_kernel<TO, G>, grid, dim3(128), smem, stream, (const bf16*)A, lda, pair_at, top, by_token, \
-              (const bf16*)W1, (const bf16*)W2, (TO*)out, N, K, meta, E, act);                                    \
+              (const bf16*)W1, (const bf16*)W2, (TO*)out, N, K, meta, E, act, in_scale);                          \
   } while (0)
     if (out_dtype == QD_BF16) { if (gated) MM_GO(bf16, true); else MM_GO(bf16, false); }
     else if (out_dtype == QD_F32) { if (gated) MM_GO(float, true); else MM_GO(float, false); }
@@ -640,7 +653,7 @@ extern "C" int qd_moe_gemm(const void* A, long long lda, int a_dtype, const int*
   }
 #define MOE_GO(TI, TW, TO, TM, G)                                                                                   \
   qd_launch(moe_gemm_kernel<TI, TW, TO, TM, G>, grid, dim3(256), 0, stream, (const TI*)A, lda, pair_at, top, by_token, \
-            (const TW*)W1, (const TW*)W2, (TO*)out, N, K, meta, E, act)
+            (const TW*)W1, (const TW*)W2, (TO*)out, N, K, meta, E, act, in_scale)
 #define MOE_PICK(TI, TW, TO)                                                     \
   do {                                                                           \
     if (tile_rows == 16) { if (gated) MOE_GO(TI, TW, TO, 16, true); else MOE_GO(TI, TW, TO, 16, false); } \

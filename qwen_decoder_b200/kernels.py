@@ -708,7 +708,7 @@ def latent_prep(u: torch.Tensor, q_off: int, q_rank: int, kv_off: int, r: int, d
     """From the float32 projections u [T, *]: cq [T, q_rank] = RMS norm of the query latent times its weight, and
     the cache row [normed latent (r) | rotated key part (dr)] written to each token's slot of ``cache``
     [pages, page_size, r + dr].  Norms and rotation in float32; ``rot_dims`` leading elements of the key part turn,
-    pairs (2i, 2i + 1)."""
+    pairs (2i, 2i + 1).  ``q_rank`` 0: there is no query latent (``cq`` is empty, ``wq_norm`` unused)."""
     T = u.shape[0]
     assert u.dtype == torch.float32 and u.stride(1) == 1 and cq.shape == (T, q_rank) and cq.dtype == cache.dtype
     assert cache.shape[-1] == r + dr and wq_norm.dtype == wkv_norm.dtype == torch.float32
@@ -729,10 +729,10 @@ def latent_absorb(q: torch.Tensor, wuk: torch.Tensor, qcat: torch.Tensor, H: int
     assert pre is None or (pre.dtype == torch.float32 and pre.shape == (H, q.shape[0], r) and pre.is_contiguous())
     T = q.shape[0]
     assert q.dtype == torch.float32 and q.shape == (T, H * (dn + dr)) and wuk.shape == (H * dn, r)
-    assert qcat.dtype == torch.float32 and qcat.shape == (T, H, r + dr)
-    _contig(q, "q"); _contig(wuk, "wuk"); _contig(qcat, "qcat")
+    assert qcat.dtype == torch.float32 and qcat.shape == (T, H, r + dr) and q.stride(1) == 1   # q: a column range is fine
+    _contig(wuk, "wuk"); _contig(qcat, "qcat")
     _check(library("latent_attention").qd_latent_absorb(
-        _ptr(q), _ptr(wuk), _I(dtype_code(wuk.dtype)), _ptr(qcat), _I(T), _I(H), _I(dn), _I(dr), _I(r), _ptr(cos),
+        _ptr(q), _LL(q.stride(0)), _ptr(wuk), _I(dtype_code(wuk.dtype)), _ptr(qcat), _I(T), _I(H), _I(dn), _I(dr), _I(r), _ptr(cos),
         _ptr(sin), _I(rot_dims), _ptr(positions), _ptr(pre), _stream()), "latent_absorb")
 
 
@@ -822,7 +822,7 @@ def mamba_gate_norm(y: torch.Tensor, u: torch.Tensor, z_off: int, w: torch.Tenso
 # ------------------------------------------------------------------ routed experts
 ACT_SILU, ACT_CLAMPED = 0, 1     # gated activations: silu(g) * u; the clamped gate (see ``gated_act``)
 MOE_MAX_TOP = 32
-MOE_ROUTE_TOP_SOFTMAX, MOE_ROUTE_SOFTMAX_ALL = 0, 1
+MOE_ROUTE_TOP_SOFTMAX, MOE_ROUTE_SOFTMAX_ALL, MOE_ROUTE_TOP_SIGMOID = 0, 1, 2
 MOE_FEW_ROWS = 8          # rows of one expert that the weight-streaming grouped product takes as one tile
 
 
@@ -842,8 +842,9 @@ def moe_route(h: torch.Tensor, wr: torch.Tensor, br: Optional[torch.Tensor], wsg
               correction: Optional[torch.Tensor] = None) -> None:
     """idx, wt [T, top] from the float32 logits wr h (+ br).  ``MOE_ROUTE_TOP_SOFTMAX``: the ``top`` largest logits and
     the softmax over those.  ``MOE_ROUTE_SOFTMAX_ALL``: scores = softmax over all outputs; the ``top`` largest of
-    score + correction are chosen and weigh by their plain scores.  sgate[t] = sigmoid(wsg . h[t]) when a shared
-    expert's gate vector is given."""
+    score + correction are chosen and weigh by their plain scores.  ``MOE_ROUTE_TOP_SIGMOID``: the ``top`` largest
+    logits, each weighed by its own sigmoid.  sgate[t] = sigmoid(wsg . h[t]) when a shared expert's gate vector is
+    given."""
     T, D = h.shape
     E = wr.shape[0]
     assert wr.shape == (E, D) and wr.dtype == h.dtype
@@ -885,28 +886,33 @@ def moe_sort(idx: torch.Tensor, E: int, tile_rows: int, max_tiles: int, place: t
 
 def moe_gemm(a: torch.Tensor, pair_at: torch.Tensor, top: int, by_token: bool, w1: torch.Tensor,
              w2: Optional[torch.Tensor], out: torch.Tensor, meta: torch.Tensor, tile_rows: int, max_tiles: int,
-             num_outputs: Optional[int] = None, act: int = ACT_SILU, limit: float = 0.0, alpha: float = 1.0) -> None:
+             num_outputs: Optional[int] = None, act: int = ACT_SILU, limit: float = 0.0, alpha: float = 1.0,
+             in_scale: Optional[torch.Tensor] = None) -> None:
     """Grouped product over the sorted pairs: out[place] = a_row W1[e]^T (or, with w2, act(a W1[e]^T, a W2[e]^T):
     silu(g) * u, or the clamped gate of ``gated_act``); a_row = a[token of the pair] when ``by_token`` else a[place];
-    w [E, N, K].  ``num_outputs``: how many outputs the router has (``meta`` is laid out by it), if more than E."""
+    w [E, N, K].  ``num_outputs``: how many outputs the router has (``meta`` is laid out by it), if more than E.
+    ``in_scale`` (float32, one per pair in the router's order): the pair's input row counts times this number, that
+    is, its sums are multiplied by it before the gate."""
     E, N, K = w1.shape
+    assert in_scale is None or (in_scale.dtype == torch.float32 and in_scale.is_contiguous())
     assert a.shape[1] == K and a.stride(1) == 1 and out.shape[1] == N and (w2 is None or w2.shape == w1.shape)
     _contig(w1, "w1"); _contig(out, "out")
     _check(library("moe").qd_moe_gemm(
         _ptr(a), _LL(a.stride(0)), _I(dtype_code(a.dtype)), _ptr(pair_at), _I(top), _I(1 if by_token else 0), _ptr(w1),
         _ptr(w2), _I(dtype_code(w1.dtype)), _ptr(out), _I(dtype_code(out.dtype)), _I(N), _I(K), _ptr(meta),
         _I(E if num_outputs is None else num_outputs), _I(tile_rows), _I(max_tiles), _I(1 if w2 is not None else 0),
-        _I(act), _F(limit), _F(alpha), _stream()), "moe_gemm")
+        _I(act), _F(limit), _F(alpha), _ptr(in_scale), _stream()), "moe_gemm")
 
 
-def moe_combine(y: torch.Tensor, place: torch.Tensor, wt: torch.Tensor, shared: Optional[torch.Tensor],
+def moe_combine(y: torch.Tensor, place: torch.Tensor, wt: Optional[torch.Tensor], shared: Optional[torch.Tensor],
                 sgate: Optional[torch.Tensor], out: torch.Tensor, idx: Optional[torch.Tensor] = None,
-                with_weights: int = 0, h: Optional[torch.Tensor] = None) -> None:
+                with_weights: int = 0, h: Optional[torch.Tensor] = None, top: Optional[int] = None) -> None:
     """out[t] = sum_k wt[t, k] y[place[t, k]] + sgate[t] * shared[t] (shared [T, D], or float32 partial sums
     [n, T, D]; without ``sgate`` the shared expert counts in full); out float32.  With ``idx`` and ``h``: a pair
-    whose expert index is ``with_weights`` or more is an identity expert and contributes wt * h[t]."""
+    whose expert index is ``with_weights`` or more is an identity expert and contributes wt * h[t].  ``wt`` None
+    (then ``top`` says how many pairs a token has): the pairs' outputs are added as they are."""
     T, D = out.shape
-    top = wt.shape[1]
+    top = wt.shape[1] if wt is not None else int(top)
     assert y.dtype == torch.float32 and out.dtype == torch.float32 and y.shape[1] == D
     n_parts, stride = 1, 0
     if shared is not None:
@@ -921,6 +927,137 @@ def moe_combine(y: torch.Tensor, place: torch.Tensor, wt: torch.Tensor, shared: 
         _ptr(y), _ptr(place), _ptr(wt), _I(top), _ptr(shared), _I(dtype_code(shared.dtype) if shared is not None else 0),
         _I(n_parts), _LL(stride), _ptr(sgate), _ptr(out), _I(T), _I(D), _ptr(idx if h is not None else None),
         _I(with_weights), _ptr(h), _I(dtype_code(h.dtype) if h is not None else 0), _stream()), "moe_combine")
+
+
+# ------------------------------------------------------------------ gated branches, short convolutions
+def gated_add_norm(x: torch.Tensor, delta: Optional[torch.Tensor], gate: Optional[torch.Tensor],
+                   weight: Optional[torch.Tensor] = None, out: Optional[torch.Tensor] = None, eps: float = 0.0,
+                   rows: Optional[torch.Tensor] = None, write_back: bool = True) -> None:
+    """x += sigmoid(gate) * delta, element by element (x float32 [T, D]; gate float32 logits [T, D] or None; delta
+    [T, D], or float32 partial sums [n, T, D]); with ``weight`` also out[r] = x[s] / sqrt(mean(x[s]^2) + eps) * weight,
+    s = rows[r] (or r).  ``write_back`` False leaves x as it was (the norm still sees the sum)."""
+    T, D = x.shape
+    assert x.dtype == torch.float32 and (gate is None or (gate.dtype == torch.float32 and gate.shape == x.shape))
+    _contig(x, "x")
+    n_parts = 1
+    if delta is not None:
+        if delta.dim() == 3:
+            n_parts = delta.shape[0]
+            assert delta.dtype == torch.float32 and tuple(delta.shape[1:]) == (T, D)
+        else:
+            assert delta.shape == x.shape
+        _contig(delta, "delta")
+    if gate is not None:
+        _contig(gate, "gate")
+    n_rows = T
+    if weight is not None:
+        n_rows = out.shape[0]
+        assert weight.dtype == torch.float32 and weight.numel() == D and out.shape[1] == D and out.is_contiguous()
+        assert rows is None or (rows.dtype == torch.int32 and rows.numel() == n_rows)
+    _check(library("gated_block").qd_gated_add_norm(
+        _ptr(x), _ptr(delta), _I(dtype_code(delta.dtype) if delta is not None else 0), _I(n_parts), _LL(T * D),
+        _ptr(gate), _ptr(weight), _ptr(out), _I(dtype_code(out.dtype) if out is not None else 0), _ptr(rows),
+        _I(n_rows), _I(D), _F(eps), _I(1 if write_back else 0), _stream()), "gated_add_norm")
+
+
+def short_conv(u: torch.Tensor, w: torch.Tensor, state: Optional[torch.Tensor], state_off: int,
+               token_req: torch.Tensor, cu_tokens: torch.Tensor, slots: torch.Tensor, out: torch.Tensor,
+               n_requests: int, residual: bool, update_state: bool) -> None:
+    """out[t, c] = (u[t, c] if ``residual``) + sum_j w[c, j] u[t - taps + 1 + j, c] within each request of the flat
+    batch; inputs before a portion come from the request's row of ``state`` (float32 [slots, n]; this convolution's
+    (taps - 1) x C kept inputs, oldest first, at ``state_off``), which is moved on by the portion when
+    ``update_state``.  u [T, C] (a column range is fine), w float32 [C, taps]."""
+    T, C = u.shape
+    taps = w.shape[1]
+    assert w.shape == (C, taps) and w.dtype == torch.float32 and w.is_contiguous() and u.stride(1) == 1
+    assert out.shape == (T, C) and out.stride(1) == 1
+    assert taps == 1 or (state is not None and state.dtype == torch.float32 and state.is_contiguous())
+    _check(library("gated_block").qd_short_conv(
+        _ptr(u), _I(dtype_code(u.dtype)), _LL(u.stride(0)), _I(C), _I(taps), _ptr(w), _ptr(state),
+        _LL(state.stride(0) if state is not None else 0), _LL(state_off), _ptr(token_req), _ptr(cu_tokens), _ptr(slots),
+        _ptr(out), _I(dtype_code(out.dtype)), _LL(out.stride(0)), _I(T), _I(n_requests), _I(1 if residual else 0),
+        _I(1 if update_state else 0), _stream()), "short_conv")
+    if update_state and taps > 1:
+        _launch_count[0] += 1
+
+
+def concat_round(a: torch.Tensor, b: torch.Tensor, out: torch.Tensor) -> None:
+    """out[t] = [a[t] | b[t]] in out's dtype; a, b float32 [T, D]."""
+    T, D = a.shape
+    assert a.dtype == b.dtype == torch.float32 and b.shape == a.shape and out.shape == (T, 2 * D)
+    _contig(a, "a"); _contig(b, "b"); _contig(out, "out")
+    _check(library("gated_block").qd_concat_round(_ptr(a), _ptr(b), _ptr(out), _I(dtype_code(out.dtype)), _I(T), _I(D),
+                                                  _stream()), "concat_round")
+
+
+ACT_GELU_TANH = 0       # plain (ungated) activations of ``plain_act``
+
+
+def plain_act(z: torch.Tensor, out: torch.Tensor, act: int = ACT_GELU_TANH) -> None:
+    """out = act(z) element by element; z float32 [T, F], or float32 partial sums [n, T, F] that are added up first."""
+    n_parts = z.shape[0] if z.dim() == 3 else 1
+    assert z.dtype == torch.float32 and tuple(z.shape[-2:]) == tuple(out.shape)
+    _contig(z, "z"); _contig(out, "out")
+    _check(library("gated_block").qd_plain_act(_ptr(z), _I(n_parts), _LL(out.numel()), _ptr(out),
+                                               _I(dtype_code(out.dtype)), _LL(out.numel()), _I(act), _stream()),
+           "plain_act")
+
+
+# ------------------------------------------------------------------ differential attention
+def diff_conv_write(u: torch.Tensor, H: int, G: int, d: int, vd: int, w: Optional[torch.Tensor],
+                    state: Optional[torch.Tensor], state_off: int, token_req: torch.Tensor, cu_tokens: torch.Tensor,
+                    slots: torch.Tensor, q_out: torch.Tensor, kv: torch.Tensor, slot_map: torch.Tensor, page_size: int,
+                    n_requests: int, write: bool) -> None:
+    """The stacked projection u (float32 [T, >= C], C = H * 2d + G * 2d + G * vd) through a short causal convolution
+    per channel (w float32 [C, taps], or None for none; the kept inputs in the requests' rows of ``state`` at
+    ``state_off``): q_out [T, H * 2d] dense, keys and values to each token's slot of the paged cache ``kv`` (a page:
+    keys [G, page_size, 2d], then values [G, page_size, vd]).  With ``write`` the cache is written and the state
+    moved on."""
+    T = u.shape[0]
+    C = H * 2 * d + G * 2 * d + G * vd
+    taps = w.shape[1] if w is not None else 0
+    assert u.dtype == torch.float32 and u.stride(1) == 1 and u.shape[1] >= C
+    assert w is None or (w.shape == (C, taps) and w.dtype == torch.float32 and w.is_contiguous())
+    assert q_out.shape == (T, H * 2 * d) and q_out.dtype == kv.dtype
+    assert taps <= 1 or (state is not None and state.dtype == torch.float32 and state.is_contiguous())
+    _contig(q_out, "q_out"); _contig(kv, "kv")
+    _check(library("attention_diff").qd_diff_conv_write(
+        _ptr(u), _LL(u.stride(0)), _I(H), _I(G), _I(d), _I(vd), _I(taps), _ptr(w), _ptr(state),
+        _LL(state.stride(0) if state is not None else 0), _LL(state_off), _ptr(token_req), _ptr(cu_tokens), _ptr(slots),
+        _ptr(q_out), _ptr(kv), _I(dtype_code(kv.dtype)), _ptr(slot_map), _I(page_size), _I(T), _I(n_requests),
+        _I(1 if write else 0), _stream()), "diff_conv_write")
+    if write and taps > 1:
+        _launch_count[0] += 1
+
+
+def diff_attention_generic(q: torch.Tensor, out: torch.Tensor, kv: torch.Tensor, block_table: torch.Tensor,
+                           token_req: torch.Tensor, positions: torch.Tensor, H: int, G: int, d: int, vd: int,
+                           page_size: int, scale: float, cap: float, lam: float, eps: float, out_scale: float,
+                           window: int, gate: Optional[torch.Tensor]) -> None:
+    """Differential attention, one warp per (token, head), float32 arithmetic, any sizes: two softmax maps over the
+    same values, o = a1 - lam * a2, divided by its root mean square over the head, times ``out_scale`` and
+    sigmoid(gate[t, h]).  q [T, H * 2d], out [T, H * vd] in the cache's dtype; gate float32 [T, H] logits (a column
+    range of a wider buffer is fine) or None."""
+    T = q.shape[0]
+    assert q.shape == (T, H * 2 * d) and out.shape == (T, H * vd) and q.dtype == out.dtype == kv.dtype
+    assert gate is None or (gate.dtype == torch.float32 and gate.shape == (T, H) and gate.stride(1) == 1)
+    _contig(q, "q"); _contig(out, "out"); _contig(kv, "kv"); _contig(block_table, "block_table")
+    _check(library("attention_diff").qd_diff_attention_generic(
+        _ptr(q), _ptr(out), _ptr(kv), _I(dtype_code(kv.dtype)), _ptr(block_table), _I(block_table.shape[1]),
+        _ptr(token_req), _ptr(positions), _I(T), _I(H), _I(G), _I(d), _I(vd), _I(page_size), _F(scale), _F(cap),
+        _F(lam), _F(eps), _F(out_scale), _I(window), _ptr(gate), _LL(gate.stride(0) if gate is not None else 0),
+        _stream()), "diff_attention_generic")
+
+
+DIFF_MAX_VDIM = 512
+
+
+def diff_attention(q: torch.Tensor, out: torch.Tensor, kv: torch.Tensor, ctx, group, H: int, G: int, d: int, vd: int,
+                   scale: float, cap: float, lam: float, eps: float, out_scale: float, window: int,
+                   gate: Optional[torch.Tensor]) -> None:
+    """Differential attention for the step ``ctx`` over the paged cache of ``group``: the kernel for these sizes."""
+    diff_attention_generic(q, out, kv, group.block_table, ctx.token_request, ctx.positions, H, G, d, vd,
+                           group.page_size, scale, cap, lam, eps, out_scale, window, gate)
 
 
 # ------------------------------------------------------------------ tanh norm, gated activations, token gate

@@ -59,13 +59,18 @@ class ResidualStream:
         self.delta_scale: Optional[torch.Tensor] = None     # float32 [D]: a layer scale on the pending branch
         self.delta_unit = None                              # (u, eps): the pending branch joins unit-normalised
         self.delta2: Optional[torch.Tensor] = None          # a second pending branch (plain)
+        self.delta_gate: Optional[torch.Tensor] = None      # float32 logits [T, D]: the pending branch joins times their sigmoid
+        self.origin: Optional[torch.Tensor] = None          # the embedding output, kept when a block reads it again
 
-    def push(self, delta: torch.Tensor, scale: Optional[torch.Tensor] = None, unit=None) -> None:
-        """Hand over a branch output (times ``scale`` along D, if given); what is still pending is added first."""
+    def push(self, delta: torch.Tensor, scale: Optional[torch.Tensor] = None, unit=None,
+             gate: Optional[torch.Tensor] = None) -> None:
+        """Hand over a branch output (times ``scale`` along D, or times sigmoid(``gate``) element by element, if
+        given); what is still pending is added first."""
         self.flush()
         self.delta = delta
         self.delta_scale = scale
         self.delta_unit = unit
+        self.delta_gate = gate
 
     def push_pair(self, delta: torch.Tensor, delta2: torch.Tensor) -> None:
         """Hand over the outputs of two branches that read the same x."""
@@ -82,17 +87,22 @@ class ResidualStream:
         return out
 
     def clear(self) -> None:
-        self.delta = self.delta_scale = self.delta_unit = self.delta2 = None
+        self.delta = self.delta_scale = self.delta_unit = self.delta2 = self.delta_gate = None
 
-    def settle(self) -> None:
-        """Add what only ``flush`` can add (a second output, a unit-normalised one); a plain pending delta stays."""
-        if self.delta2 is not None or self.delta_unit is not None:
+    def settle(self, gated_ok: bool = False) -> None:
+        """Add what only ``flush`` can add (a second output, a unit-normalised one, and -- unless the caller's own
+        kernel takes it, ``gated_ok`` -- a gated one); a plain pending delta stays."""
+        if self.delta2 is not None or self.delta_unit is not None or (self.delta_gate is not None and not gated_ok):
             self.flush()
 
     def flush(self) -> None:
         if self.delta is None and self.delta2 is None:
             return
-        if self.delta2 is None and self.delta_unit is None:
+        if self.delta_gate is not None:
+            if self.delta2 is not None or self.delta_unit is not None or self.delta_scale is not None:
+                raise ValueError("a gated branch beside a second, a scaled or a unit-normalised one is not supported")
+            kernels.gated_add_norm(self.x, self.delta, self.delta_gate)
+        elif self.delta2 is None and self.delta_unit is None:
             kernels.residual_add(self.x, self.delta, self.delta_scale)
         else:
             if self.delta_scale is not None:
@@ -114,6 +124,17 @@ class StateCacheView:
     """A mixer's view of its fixed-size per-request state in this step."""
     state: torch.Tensor         # [slots, *shape]
     write: bool
+
+
+@dataclass
+class RunCacheView:
+    """What a run of a layer sees when its need is a tuple: its pages and its per-request state row.  The owner of
+    the need splits the row among its users by offset (a block keeps a convolution's inputs at the row's end, say,
+    and hands the mixer a view with ``state_off`` / ``state_len`` set to the mixer's share)."""
+    paged: Optional[PagedCacheView]
+    state: Optional[StateCacheView]
+    state_off: int = 0
+    write: bool = True
 
 
 class Mixer(Part):

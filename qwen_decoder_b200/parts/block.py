@@ -4,14 +4,17 @@ A branch's output is left pending on the stream and added by the next norm's ker
 """
 from __future__ import annotations
 
+import math
 from typing import Dict, List
 
 import torch
 
+from ..cache import FixedState
 from ..config.registry import register_part
 from ..weights.loader import TensorSource, TensorSpec
 from .. import kernels
-from .base import Block, FeedForward, Mixer, Norm, ResidualStream
+from .base import Block, FeedForward, Mixer, Norm, ResidualStream, RunCacheView
+from . import matmul_backend
 from .linear import Linear
 
 
@@ -193,3 +196,146 @@ class ParallelSideBlock(Block):
         g = torch.empty((T, self.side_dim), dtype=self.dtype, device=dev)
         kernels.token_gate(self.gate.forward(xr, out_dtype=torch.float32), self.side_rows, ctx.tokens, g)
         stream.push(self.proj.forward_partial(g), unit=(self.side_norm, self.eps))
+
+
+@register_part("block", "pre_norm_gated")
+class GatedPreNormBlock(Block):
+    """The pre-norm block whose branches join through a gate, and whose mixer reads its input through a short
+    causal convolution over time:
+
+        h = norm1(x);   x += sigmoid(Wg1 h + b1) * mixer(h + conv(h));
+        h = norm2(x);   x += sigmoid(Wg2 h + b2) * feed_forward(h)               (a layer may have no feed-forward)
+        conv(h)_t = sum_j w[:, j] * h_(t - taps + 1 + j), zeros before the sequence's start     (per channel, no bias)
+
+    The gates read the normed input itself, before the convolution.  ``taps`` = 0 leaves the convolution out; with
+    more than one tap the last taps - 1 inputs h of every request are part of its state: the block adds
+    (taps - 1) x size float32 numbers to the run's per-request state row, after whatever the mixer keeps there.
+    Tensors: ``<prefix>canon1`` [size, taps], ``<prefix>rg1`` [size, size] with ``<prefix>rg1.b``, and ``rg2`` alike.
+    A branch's output waits on the stream with its gate's logits; the next norm's kernel multiplies, adds and norms."""
+    norm_roles = ("input", "post_mixer")
+
+    def __init__(self, mixer: Mixer, feed_forward, norms: Dict[str, Norm], size: int, taps: int = 0, prefix: str = "",
+                 conv_name: str = "canon1", gate_names=("rg1", "rg2")):
+        if "input" not in norms or (feed_forward is not None and "post_mixer" not in norms):
+            raise ValueError("pre_norm_gated block needs the norms 'input' and, with a feed-forward, 'post_mixer'")
+        if taps < 0:
+            raise ValueError("pre_norm_gated block: taps must be 0 (no convolution) or more")
+        self.mixer, self.feed_forward = mixer, feed_forward
+        self.norm1 = norms["input"]
+        self.norm2 = norms.get("post_mixer") if feed_forward is not None else None
+        self.size, self.taps, self.prefix, self.conv_name = size, int(taps), prefix, conv_name
+        self.gate1 = Linear(size, [(f"{prefix}{gate_names[0]}", size)], bias=True, weight_suffix="", bias_suffix=".b")
+        self.gate2 = Linear(size, [(f"{prefix}{gate_names[1]}", size)], bias=True, weight_suffix="",
+                            bias_suffix=".b") if feed_forward is not None else None
+        self.conv_w = None
+        self._mixer_need = mixer.cache_need()
+        parts = self._mixer_need if isinstance(self._mixer_need, tuple) else \
+            (self._mixer_need,) if self._mixer_need is not None else ()
+        self._paged = [p for p in parts if not isinstance(p, FixedState)]
+        fixed = [p for p in parts if isinstance(p, FixedState)]
+        if any(f.dtype != torch.float32 for f in fixed) or len(fixed) > 1:
+            raise ValueError("pre_norm_gated block: the mixer's per-request state must be one float32 row")
+        self.state_off = math.prod(fixed[0].shape) if fixed else 0       # the block's share follows the mixer's
+
+    def cache_need(self):
+        if self.taps <= 1:
+            return self._mixer_need
+        return tuple(self._paged) + (FixedState((self.state_off + (self.taps - 1) * self.size,), torch.float32),)
+
+    def parts(self):
+        return [p for p in (self.norm1, self.mixer, self.norm2, self.feed_forward) if p is not None]
+
+    def tensor_specs(self) -> List[TensorSpec]:
+        specs = [s for p in self.parts() for s in p.tensor_specs()]
+        specs += self.gate1.tensor_specs()
+        if self.gate2 is not None:
+            specs += self.gate2.tensor_specs()
+        if self.taps:
+            specs.append(TensorSpec(f"{self.prefix}{self.conv_name}", (self.size, self.taps), init="uniform:-0.5:0.5"))
+        return specs
+
+    def bind(self, source: TensorSource, dtype: torch.dtype, device: torch.device) -> None:
+        self.dtype = dtype
+        for p in self.parts():
+            p.bind(source, dtype, device)
+        self.gate1.bind(source, dtype, device)
+        if self.gate2 is not None:
+            self.gate2.bind(source, dtype, device)
+        if self.taps:
+            self.conv_w = source.get(f"{self.prefix}{self.conv_name}").to(device=device, dtype=torch.float32).contiguous()
+
+    def _mixer_cache(self, cache):
+        """The mixer's own view: what it would get in a block without a state of its own."""
+        if self.taps <= 1 or not isinstance(cache, RunCacheView):
+            return cache
+        if isinstance(self._mixer_need, tuple):
+            return cache                                # pages and the row; the mixer's share starts at 0
+        if isinstance(self._mixer_need, FixedState):
+            return cache.state
+        return cache.paged                              # None for a mixer that caches nothing
+
+    def forward(self, stream: ResidualStream, ctx, cache) -> None:
+        h = self.norm1.forward(stream, self.dtype)
+        hm = h
+        if self.taps:
+            hm = torch.empty_like(h)
+            st = cache.state if self.taps > 1 else None
+            kernels.short_conv(h, self.conv_w, st.state if st is not None else None, self.state_off, ctx.token_request,
+                               ctx.cu_tokens, ctx.state_slots, hm, ctx.num_requests, residual=True,
+                               update_state=bool(st is not None and st.write))
+        g = self.gate1.forward(h, out_dtype=torch.float32)
+        stream.push(self.mixer.forward(hm, ctx, self._mixer_cache(cache)), gate=g)
+        if self.feed_forward is not None:
+            h = self.norm2.forward(stream, self.dtype)
+            g = self.gate2.forward(h, out_dtype=torch.float32)
+            stream.push(self.feed_forward.forward(h, ctx), gate=g)
+
+
+@register_part("block", "loop_input")
+class LoopInput(Block):
+    """What stands before every pass of a loop of layers: the residual sum takes the embedding output x0 in again
+    and a per-pass vector is added,
+
+        x <- Win [x ; x0] + step[visit]          Win [size, 2 size] (x's half first), step [passes, size]
+
+    It has no mixer, no feed-forward and no cache; the schedule names it once per pass and says which (``visit``).
+    The product takes x and x0 rounded to the engine's dtype and leaves float32 sums, which become the new x."""
+    takes_visit = True
+    reads_embedding_output = True
+
+    def __init__(self, mixer, feed_forward, norms, size: int, passes: int, prefix: str = "",
+                 names=("loop.in", "loop.step")):
+        if mixer is not None or feed_forward is not None or norms:
+            raise ValueError("loop_input block takes no mixer, feed-forward or norm")
+        self.mixer = self.feed_forward = None
+        self.size, self.passes, self.prefix, self.names = size, int(passes), prefix, tuple(names)
+        self.inp = Linear(2 * size, [(f"{prefix}{names[0]}", size)], bias=False, weight_suffix="")
+        self.step = None
+
+    def cache_need(self):
+        return None
+
+    def parts(self):
+        return []
+
+    def tensor_specs(self) -> List[TensorSpec]:
+        return self.inp.tensor_specs() + [TensorSpec(f"{self.prefix}{self.names[1]}", (self.passes, self.size),
+                                                     init="around_zero")]
+
+    def bind(self, source: TensorSource, dtype: torch.dtype, device: torch.device) -> None:
+        self.dtype = dtype
+        self.inp.bind(source, dtype, device)
+        self.step = source.get(f"{self.prefix}{self.names[1]}").to(device=device, dtype=torch.float32).contiguous()
+
+    def forward(self, stream: ResidualStream, ctx, cache, visit: int = 0) -> None:
+        if stream.origin is None:
+            raise ValueError("loop_input block: the model did not keep the embedding output")
+        if not (0 <= visit < self.passes):
+            raise ValueError(f"loop_input block: pass {visit} of {self.passes}")
+        stream.flush()
+        T = stream.x.shape[0]
+        both = torch.empty((T, 2 * self.size), dtype=self.dtype, device=stream.x.device)
+        kernels.concat_round(stream.x, stream.origin, both)
+        x = torch.empty((T, self.size), dtype=torch.float32, device=stream.x.device)
+        matmul_backend.linear(both, self.inp.weight, self.step[visit], x)     # the pass's vector rides as the bias
+        stream.x = x

@@ -13,6 +13,10 @@ Keys and values are never expanded: the query is carried into the latent space (
 over the cached rows, and Wuv_h is applied to the weighted sum of latents (``csrc/latent_attention.cu``).  Wdq,
 Wdkv and Wg are one stacked product of h.  Norms, angles, scores and softmax weights are float32 in both engine
 dtypes.  The plain norms here multiply by the stored weight (no offset); their eps is the layer's.
+
+Variants, all constructor parameters: ``q_rank`` = 0 leaves the query latent out, q = Wq h (tensor ``<prefix>q``);
+``rope_dim`` = 0 leaves the rotated part out (no position enters the scores, the cached row is c alone);
+``output_gate`` = False leaves the sigmoid gate out.
 """
 from __future__ import annotations
 
@@ -53,7 +57,7 @@ def attend_splits(ctas_without_split: int, max_keys: int) -> int:
 class LatentAttention(Mixer):
     def __init__(self, hidden_size: int, num_heads: int, nope_dim: int, rope_dim: int, v_dim: int, q_rank: int,
                  kv_rank: int, scale: float, eps: float, position=None, window: Optional[int] = None,
-                 prefix: str = "self_attn.", weight_suffix: str = ".weight"):
+                 prefix: str = "self_attn.", weight_suffix: str = ".weight", output_gate: bool = True):
         if kv_rank > kernels.LATENT_MAX_RANK:
             raise ValueError(f"latent attention: kv_rank {kv_rank} exceeds {kernels.LATENT_MAX_RANK}")
         self.hidden_size, self.num_heads = hidden_size, num_heads
@@ -63,10 +67,15 @@ class LatentAttention(Mixer):
         self.position = position            # a Rotary over the rope part (its rotary_dim leading elements turn) or None
         self.prefix, self.sfx = prefix, weight_suffix
         H = num_heads
-        self.down = Linear(hidden_size, [(f"{prefix}dq", q_rank), (f"{prefix}dkv", kv_rank + rope_dim),
-                                         (f"{prefix}g", H * v_dim)], bias=False, weight_suffix=weight_suffix)
+        self.output_gate = bool(output_gate)
+        self.q_width = q_rank if q_rank else H * (nope_dim + rope_dim)      # the stacked product's first columns
+        pieces = [(f"{prefix}dq", q_rank) if q_rank else (f"{prefix}q", self.q_width),
+                  (f"{prefix}dkv", kv_rank + rope_dim)]
+        if self.output_gate:
+            pieces.append((f"{prefix}g", H * v_dim))
+        self.down = Linear(hidden_size, pieces, bias=False, weight_suffix=weight_suffix)
         self.up_q = Linear(q_rank, [(f"{prefix}uq", H * (nope_dim + rope_dim))], bias=False,
-                           weight_suffix=weight_suffix)
+                           weight_suffix=weight_suffix) if q_rank else None
         self.out = Linear(H * v_dim, [(f"{prefix}o", hidden_size)], bias=False, weight_suffix=weight_suffix)
 
     def cache_need(self):
@@ -74,18 +83,22 @@ class LatentAttention(Mixer):
 
     def tensor_specs(self) -> List[TensorSpec]:
         p, s, H = self.prefix, self.sfx, self.num_heads
-        return self.down.tensor_specs() + self.up_q.tensor_specs() + self.out.tensor_specs() + [
-            TensorSpec(f"{p}dq.norm", (self.q_rank,), init="around_one"),
+        specs = self.down.tensor_specs() + self.out.tensor_specs()
+        if self.q_rank:
+            specs += self.up_q.tensor_specs() + [TensorSpec(f"{p}dq.norm", (self.q_rank,), init="around_one")]
+        return specs + [
             TensorSpec(f"{p}dkv.norm", (self.kv_rank,), init="around_one"),
             TensorSpec(f"{p}uk{s}", (H * self.nope_dim, self.kv_rank)),
             TensorSpec(f"{p}uv{s}", (H * self.v_dim, self.kv_rank))]
 
     def bind(self, source: TensorSource, dtype: torch.dtype, device: torch.device) -> None:
         for lin in (self.down, self.up_q, self.out):
-            lin.bind(source, dtype, device)
+            if lin is not None:
+                lin.bind(source, dtype, device)
         p, s = self.prefix, self.sfx
         f32 = lambda n: source.get(n).to(device=device, dtype=torch.float32).contiguous()
-        self.w_dq_norm, self.w_dkv_norm = f32(f"{p}dq.norm"), f32(f"{p}dkv.norm")
+        self.w_dkv_norm = f32(f"{p}dkv.norm")
+        self.w_dq_norm = f32(f"{p}dq.norm") if self.q_rank else self.w_dkv_norm       # unused without a query latent
         self.w_uk = source.get(f"{p}uk{s}").to(device=device, dtype=dtype).contiguous()
         self.w_uv = source.get(f"{p}uv{s}").to(device=device, dtype=dtype).contiguous()
         H = self.num_heads
@@ -102,11 +115,12 @@ class LatentAttention(Mixer):
         dn, dr, dv, r, qr = self.nope_dim, self.rope_dim, self.v_dim, self.kv_rank, self.q_rank
         pos = self.position
         rot = (pos.cos, pos.sin, pos.rotary_dim) if pos is not None else (self._no_table, self._no_table, 0)
-        u = self.down.forward(x, out_dtype=torch.float32)                   # [T, qr | r + dr | H * dv]
+        qw = self.q_width
+        u = self.down.forward(x, out_dtype=torch.float32)                   # [T, qr (or q itself) | r + dr | H * dv]
         cq = torch.empty((T, qr), dtype=x.dtype, device=x.device)
-        kernels.latent_prep(u, 0, qr, qr, r, dr, self.w_dq_norm, self.w_dkv_norm, self.eps, *rot, ctx.positions,
+        kernels.latent_prep(u, 0, qr, qw, r, dr, self.w_dq_norm, self.w_dkv_norm, self.eps, *rot, ctx.positions,
                             cache.group.slot_map, cq, cache.kv, cache.write)
-        q = self.up_q.forward(cq, out_dtype=torch.float32)
+        q = self.up_q.forward(cq, out_dtype=torch.float32) if qr else u[:, :qw]
         qcat = torch.empty((T, H, r + dr), dtype=torch.float32, device=x.device)
         library = x.dtype == torch.bfloat16 and T >= LIBRARY_TOKENS and matmul_backend.mode != "generic"
         pre = None
@@ -126,5 +140,5 @@ class LatentAttention(Mixer):
         if library:
             pre = torch.bmm(_hi_lo(o_lat), self.w_uv_twice, out_dtype=torch.float32)        # [H, T, dv]
             matmul_backend.counters["library"] += 1
-        kernels.latent_expand(o_lat, self.w_uv, u[:, qr + r + dr:], attn, dv, pre=pre)
+        kernels.latent_expand(o_lat, self.w_uv, u[:, qw + r + dr:] if self.output_gate else None, attn, dv, pre=pre)
         return self.out.forward_partial(attn)

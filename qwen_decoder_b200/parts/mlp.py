@@ -85,3 +85,34 @@ class SwiGLU(FeedForward):
         else:
             kernels.swiglu(self.gate_up.forward(x), h)
         return self.down.forward_partial(h)
+
+
+PLAIN_ACTIVATIONS = {"gelu_tanh": kernels.ACT_GELU_TANH}
+
+
+@register_part("feed_forward", "mlp")
+class PlainMLP(FeedForward):
+    """The ungated feed-forward: delta = Wdown act(Wup h), no biases; ``activation`` = "gelu_tanh" is
+    0.5 z (1 + tanh(sqrt(2 / pi) (z + 0.044715 z^3))).  The first product leaves float32 sums, one elementwise
+    kernel makes the activation in the engine's dtype."""
+
+    def __init__(self, hidden_size: int, intermediate_size: int, prefix: str = "mlp.", names: Sequence[str] = ("up", "down"),
+                 weight_suffix: str = "", activation: str = "gelu_tanh"):
+        if activation not in PLAIN_ACTIVATIONS:
+            raise ValueError(f"feed-forward: activation must be one of {sorted(PLAIN_ACTIVATIONS)}, got {activation!r}")
+        self.hidden_size, self.intermediate_size, self.activation = hidden_size, intermediate_size, activation
+        u, d = names
+        self.up = Linear(hidden_size, [(f"{prefix}{u}", intermediate_size)], bias=False, weight_suffix=weight_suffix)
+        self.down = Linear(intermediate_size, [(f"{prefix}{d}", hidden_size)], bias=False, weight_suffix=weight_suffix)
+
+    def tensor_specs(self) -> List[TensorSpec]:
+        return self.up.tensor_specs() + self.down.tensor_specs()
+
+    def bind(self, source: TensorSource, dtype: torch.dtype, device: torch.device) -> None:
+        self.up.bind(source, dtype, device)
+        self.down.bind(source, dtype, device)
+
+    def forward(self, x: torch.Tensor, ctx) -> torch.Tensor:
+        h = torch.empty((x.shape[0], self.intermediate_size), dtype=x.dtype, device=x.device)
+        kernels.plain_act(self.up.forward(x, out_dtype=torch.float32), h, PLAIN_ACTIVATIONS[self.activation])
+        return self.down.forward_partial(h)

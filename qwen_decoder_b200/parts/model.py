@@ -18,11 +18,12 @@ from ..cache import CacheLayout, FixedState, PagedKV
 from ..config.registry import create_part
 from ..config.spec import ModelSpec, PartSpec
 from ..weights.loader import TensorSource, TensorSpec
-from .base import PagedCacheView, ResidualStream, StateCacheView
+from .base import PagedCacheView, ResidualStream, RunCacheView, StateCacheView
 from .linear import Linear
 # importing the part modules registers them
 from . import attention as _attention, block as _block, mlp as _mlp, norm as _norm, rotary as _rotary  # noqa: F401
 from . import latent_attention as _latent, mamba2 as _mamba2, moe as _moe, sink_attention as _sink  # noqa: F401
+from . import diff_attention as _diff  # noqa: F401
 
 
 class DecoderModel:
@@ -35,14 +36,16 @@ class DecoderModel:
                           for name, ps in spec.positions.items()}
         self.layers = []
         for ls in spec.layers:
-            mp = dict(ls.mixer.params)
-            mp["prefix"] = ls.prefix + mp.get("prefix", "")
-            if "position" in mp:
-                pname = mp["position"]
-                if pname is not None and pname not in self.positions:
-                    raise ValueError(f"layer {ls.prefix!r}: unknown position encoding {pname!r}")
-                mp["position"] = self.positions[pname] if pname is not None else None
-            mixer = create_part("mixer", ls.mixer.name, **mp)
+            mixer = None                # a block that only works on the residual sum has no mixer
+            if ls.mixer is not None:
+                mp = dict(ls.mixer.params)
+                mp["prefix"] = ls.prefix + mp.get("prefix", "")
+                if "position" in mp:
+                    pname = mp["position"]
+                    if pname is not None and pname not in self.positions:
+                        raise ValueError(f"layer {ls.prefix!r}: unknown position encoding {pname!r}")
+                    mp["position"] = self.positions[pname] if pname is not None else None
+                mixer = create_part("mixer", ls.mixer.name, **mp)
             ff = None
             if ls.feed_forward is not None:
                 fp = dict(ls.feed_forward.params)
@@ -61,6 +64,8 @@ class DecoderModel:
             if not (0 <= e.layer < len(self.layers)):
                 raise ValueError(f"schedule entry {i} names layer {e.layer}, the model has {len(self.layers)}")
         self.schedule = list(spec.schedule)
+        # a block that reads the embedding output again (a loop that takes it in at every pass) has it kept
+        self.keeps_origin = any(getattr(layer, "reads_embedding_output", False) for layer in self.layers)
         fn = dict(spec.final_norm.params)
         fn["prefix"] = spec.final_norm_prefix + fn.get("prefix", "")
         self.final_norm = create_part("norm", spec.final_norm.name, **fn)
@@ -121,19 +126,29 @@ class DecoderModel:
         return out
 
     # ---- cache -------------------------------------------------------------
+    def _need(self, layer):
+        """What a run of this layer caches: the block's own answer where it has one (it may keep a state beside
+        its mixer's), else the mixer's."""
+        if hasattr(layer, "cache_need"):
+            return layer.cache_need()
+        return layer.mixer.cache_need() if layer.mixer is not None else None
+
     def cache_layout(self) -> CacheLayout:
-        needs = [self.layers[e.layer].mixer.cache_need() for e in self.schedule]
+        needs = [self._need(self.layers[e.layer]) for e in self.schedule]
         return CacheLayout.from_needs(needs, [e.cache_of for e in self.schedule])
 
     def _cache_view(self, i: int, ctx):
         layout = ctx.cache.layout
         write = self.schedule[i].cache_of is None
+        paged = state = None
         if i in layout.paged:
             g, _ = layout.paged[i]
-            return PagedCacheView(kv=ctx.cache.layer_kv(i), group=ctx.groups[g], write=write)
+            paged = PagedCacheView(kv=ctx.cache.layer_kv(i), group=ctx.groups[g], write=write)
         if i in layout.fixed:
-            return StateCacheView(state=ctx.cache.layer_state(i), write=write)
-        return None
+            state = StateCacheView(state=ctx.cache.layer_state(i), write=write)
+        if paged is not None and state is not None:
+            return RunCacheView(paged=paged, state=state, write=write)
+        return paged if paged is not None else state
 
     # ---- forward -------------------------------------------------------------
     def forward(self, ctx) -> torch.Tensor:
@@ -147,8 +162,14 @@ class DecoderModel:
                 return torch.empty((0, self.vocab_size), dtype=torch.float32, device=self.device)
             return self.lm_head.forward(h, out_dtype=torch.float32)
         stream = ResidualStream(x)
+        if self.keeps_origin:
+            stream.origin = x.clone()
         for i, e in enumerate(self.schedule):
-            self.layers[e.layer].forward(stream, ctx, self._cache_view(i, ctx))
+            layer = self.layers[e.layer]
+            if getattr(layer, "takes_visit", False):
+                layer.forward(stream, ctx, self._cache_view(i, ctx), visit=e.visit)
+            else:
+                layer.forward(stream, ctx, self._cache_view(i, ctx))
         if ctx.num_wanted == 0:
             return torch.empty((0, self.vocab_size), dtype=torch.float32, device=self.device)
         h = self.final_norm.forward(stream, self.dtype, rows=ctx.logit_rows)

@@ -19,14 +19,17 @@ from .base import Norm, ResidualStream
 
 @register_part("norm", "rmsnorm")
 class RMSNorm(Norm):
-    def __init__(self, size: int, eps: float, prefix: str = "", tensor: str = "weight", offset: float = 0.0):
+    def __init__(self, size: int, eps: float, prefix: str = "", tensor: str = "weight", offset: float = 0.0,
+                 gain: float = 1.0):
         """``tensor``: the scale's name after ``prefix``.  ``offset``: the stored scale is kept around
-        ``-offset`` and the norm multiplies by ``offset + w`` (1 for scales stored around zero)."""
+        ``-offset`` and the norm multiplies by ``offset + w`` (1 for scales stored around zero).  ``gain``: one more
+        constant factor on the output (a model that scales its logits by a constant puts it on the final norm)."""
         self.size = size
         self.eps = float(eps)
         self.prefix = prefix
         self.tensor = tensor
         self.offset = float(offset)
+        self.gain = float(gain)
         self.weight: Optional[torch.Tensor] = None
 
     def tensor_specs(self) -> List[TensorSpec]:
@@ -36,16 +39,23 @@ class RMSNorm(Norm):
     def bind(self, source: TensorSource, dtype: torch.dtype, device: torch.device) -> None:
         # norm scales are used in float32 whatever they are stored in; the offset is added once, here
         w = source.get(f"{self.prefix}{self.tensor}").to(device=device, dtype=torch.float32)
-        self.weight = (w + self.offset if self.offset != 0.0 else w).contiguous()
+        w = w + self.offset if self.offset != 0.0 else w
+        self.weight = (w * self.gain if self.gain != 1.0 else w).contiguous()
 
     def native_params(self) -> Optional[dict]:
         return {"kind": "rmsnorm", "weight": self.weight, "eps": self.eps, "size": self.size}
 
     def forward(self, stream: ResidualStream, out_dtype: torch.dtype,
                 rows: Optional[torch.Tensor] = None) -> torch.Tensor:
-        stream.settle()
+        stream.settle(gated_ok=True)
         n = stream.x.shape[0] if rows is None else rows.numel()
         out = torch.empty((n, self.size), dtype=out_dtype, device=stream.x.device)
+        if stream.delta_gate is not None:       # a branch that joins through a gate: added and normed in one launch
+            kernels.gated_add_norm(stream.x, stream.delta, stream.delta_gate, self.weight, out, self.eps, rows=rows,
+                                   write_back=rows is None)
+            if rows is None:
+                stream.clear()
+            return out
         kernels.add_rmsnorm(stream.x, stream.delta, self.weight, out, self.eps, rows=rows,
                             write_back=rows is None, delta_scale=stream.delta_scale)
         if rows is None:
