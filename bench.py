@@ -299,7 +299,49 @@ def veterax_configs(size, layers=None):
     return veterax, dense_cfg
 
 
-def hybrid_bench(args, label="hybrid", configs=None):
+# ---- Solopel beside Veterax at equal layer sizes -------------------------------------------------------------------
+# Eight layer runs (six layers, the first two run twice): latent attention and differential attention in turn (two maps of
+# 64 per head, so a cached key is as wide as the other model's), gated branches, input convolutions of four taps, routed
+# experts with a shared one in five layers and a dense feed-forward in one.  The other model: Veterax (attention with values
+# of a size of their own and routed experts with a shared one in every layer) with the same width, depth, heads, expert
+# sizes and vocabulary.
+SOLOPEL_SIZES = {
+    "S": dict(width=2048, vocab=32000, heads=(16, 2), dim=64, vdim=128, latent=dict(heads=16, dim=128, vdim=128, kv_rank=512),
+              ff=5632, moe=dict(experts=64, top=6, ff=1408, shared=2816)),
+    "M": dict(width=4096, vocab=32000, heads=(32, 8), dim=64, vdim=128, latent=dict(heads=32, dim=128, vdim=128, kv_rank=512),
+              ff=11008, moe=dict(experts=32, top=4, ff=2048, shared=4096)),
+}
+
+
+def solopel_configs(size, layers=None):
+    from qwen_decoder_b200.config import config_from_dict
+    z = SOLOPEL_SIZES[size]
+    H, G = z["heads"]
+    m, lat = z["moe"], z["latent"]
+    latent = {"type": "latent_attention", "mixer": dict(lat, scale=lat["dim"] ** -0.5)}
+    attn = {"type": "attention", "mixer": {"heads": H, "kv_heads": G, "dim": z["dim"], "vdim": z["vdim"], "diff": 0.3,
+                                           "conv": 4, "softcap": 50.0, "scale": z["dim"] ** -0.5}}
+    moe = {"kind": "moe", "expert": {"ff": m["ff"]}, "router": {"experts": m["experts"], "top": m["top"]},
+           "shared": {"ff": m["shared"]}}
+    dense = {"kind": "dense", "ff": z["ff"]}
+    six = [dict(latent, mlp=moe), dict(attn, mlp=moe), dict(latent, mlp=dense), dict(attn, mlp=moe), dict(latent, mlp=moe),
+           dict(attn, mlp=moe)]
+    if layers:                  # fewer layers of the same sizes (a capture under a profiler holds fewer weights)
+        six = six[:max(2, layers)]
+    solopel = config_from_dict({"architecture": "Solopel", "vocab": z["vocab"], "width": z["width"], "norm": {"eps": 1e-6},
+                                "canon": {"taps": 4}, "loop": {"start": 0, "stop": 2, "times": 2}, "logit_scale": 0.5,
+                                "layers": six})
+    vmix = {"heads": H, "kv_heads": G, "dim": 2 * z["dim"], "vdim": z["vdim"], "scale": (2 * z["dim"]) ** -0.5,
+            "rot": {"base": 1000000.0, "dims": 2 * z["dim"]}}
+    vmlp = {"kind": "moe", "expert": {"ff": m["ff"], "limit": 7.0}, "router": {"experts": m["experts"], "identity": 0,
+            "top": m["top"]}, "shared": {"ff": m["shared"], "limit": 7.0}}
+    veterax = config_from_dict({"architecture": "Veterax", "vocab": z["vocab"], "width": z["width"], "norm": {"eps": 1e-5},
+                                "token_side": {"dim": 256},
+                                "layers": [{"type": "attention", "mixer": vmix, "mlp": vmlp} for _ in range(len(six) + 2)]})
+    return solopel, veterax
+
+
+def hybrid_bench(args, label="hybrid", configs=None, other="dense"):
     """``--micro hybrid`` (and ``--micro veterax``, which passes its own pair of models): decode steps (batch 1, 8, 64 at ``--context``) and a prompt of ``--prefill-tokens`` tokens, for the
     hybrid design and for the dense decoder at equal sizes; one JSON line.  ``--only hybrid|dense`` and ``--phase`` narrow it
     (for a launch list under a profiler)."""
@@ -316,8 +358,9 @@ def hybrid_bench(args, label="hybrid", configs=None):
     gen = torch.Generator().manual_seed(1)
     clocks = ClockSampler()
     clocks.start()
-    for name, cfg in zip((label, "dense"), (configs or hybrid_configs)(args.hybrid_size)):
-        if args.only and args.only != name and not (args.only == "hybrid" and name == label):
+    for name, cfg in zip((label, other), (configs or hybrid_configs)(args.hybrid_size)):
+        if args.only and args.only != name and not (args.only == "hybrid" and name == label) and \
+                not (args.only in ("dense", "other") and name == other):
             continue
         max_b = max(batches + [1])
         span = ctxlen + 2 * (W + K) + 64
@@ -445,6 +488,8 @@ def micro(args):
         return hybrid_bench(args)
     if args.micro == "veterax":
         return hybrid_bench(args, "veterax", lambda size: veterax_configs(size, args.veterax_layers))
+    if args.micro == "solopel":
+        return hybrid_bench(args, "solopel", lambda size: solopel_configs(size, args.veterax_layers), other="veterax")
     if args.micro == "latent_attend":
         return latent_attend_micro(args)
     """One kernel alone: W-streaming contraction, decode attention or prefill attention at the 3B sizes."""
@@ -696,7 +741,7 @@ def main():
     ap.add_argument("--no-e2e", action="store_true")
     ap.add_argument("--timeline", action="store_true",
                     help="with --micro prefill_attention: print the kernel's own time stamps of one CTA (microseconds) to stderr")
-    ap.add_argument("--micro", default=None, choices=["gemm", "decode_attention", "decode_attention_rope", "prefill_attention", "serve", "mixed_step", "hybrid", "latent_attend", "veterax"],
+    ap.add_argument("--micro", default=None, choices=["gemm", "decode_attention", "decode_attention_rope", "prefill_attention", "serve", "mixed_step", "hybrid", "latent_attend", "veterax", "solopel"],
                     help="time one kernel alone at the 3B shape (for profiles/), or with 'serve' a whole run of "
                          "--batch requests (--context prompt tokens, --steps new tokens each) through the entry "
                          "point; print one JSON line and exit")
@@ -708,9 +753,9 @@ def main():
     ap.add_argument("--tokens", type=int, default=8)
     ap.add_argument("--micro-graph", action="store_true", help="gemm: time inside a replayed graph, cold weights")
     ap.add_argument("--micro-splits", type=int, default=1, help="gemm with --micro-graph: shares of K (partial sums)")
-    ap.add_argument("--hybrid-size", default="S", choices=["S", "M"], help="hybrid, veterax: which layer sizes")
-    ap.add_argument("--only", default=None, choices=["hybrid", "dense"], help="hybrid, veterax: one of the two models (hybrid = the first)")
-    ap.add_argument("--veterax-layers", type=int, default=None, help="veterax: fewer layers than the size has")
+    ap.add_argument("--hybrid-size", default="S", choices=["S", "M"], help="hybrid, veterax, solopel: which layer sizes")
+    ap.add_argument("--only", default=None, choices=["hybrid", "dense", "other"], help="hybrid, veterax, solopel: one of the two models (hybrid = the first; dense, other = the second)")
+    ap.add_argument("--veterax-layers", type=int, default=None, help="veterax, solopel: fewer layers than the size has")
     ap.add_argument("--phase", default="all", choices=["all", "decode", "prefill"], help="hybrid: decode steps, the prompt, or both")
     ap.add_argument("--history", type=int, default=2048, help="mixed_step: cached tokens before the prompt portion")
     ap.add_argument("--stamps", action="store_true",

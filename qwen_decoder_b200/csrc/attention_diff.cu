@@ -15,6 +15,7 @@
 // float32 and odd sizes; the tensor-core kernel below it serves bfloat16.
 #include "common.cuh"
 #include "short_conv.cuh"
+#include "mma_sync.cuh"
 #include <math.h>
 
 #define AD_MAX_VD 512
@@ -228,5 +229,365 @@ extern "C" int qd_diff_attention_generic(const void* q, void* out, const void* k
               page_size, window, P, gate, ldg);
   else
     return QD_ERR_UNSUPPORTED;
+  return qd_last_error();
+}
+
+// ------------------------------------------------------------------------------------------- attend, tensor cores
+// The same attention in bfloat16 on mma.sync m16n8k16 (float32 sums), for prompt portions and decoded tokens alike.
+// A CTA of four warps owns one tile of one (request, kv head): 32 (token, head within the group) pairs, each as TWO
+// rows, one per map.  Warps 0 and 1 hold the pairs' first maps, warps 2 and 3 their second maps: a warp's 16 rows
+// all read the same half of a key row (columns [map * d, map * d + d)) and the same values, so each warp is an
+// ordinary attention over 64-key tiles (16-byte cp.async, two stages, key by key through the block table: any page
+// size).  Scores, the cap and the softmax stay float32; a weight enters P V as two bfloat16 numbers (hi + lo).  Head
+// sizes are padded with zero columns in shared memory up to the template's D (64, 128) and DV (64, 128).
+// With one split the two maps of a pair meet in shared memory at the end, where the difference, its unit norm, the
+// constant and the gate are applied; with ``splits`` > 1 the key tiles are shared among gridDim.z CTAs that leave
+// (o, m, l) per (row, map) in scratch memory, and ``diff_combine_kernel`` finishes.
+#define DM_PAIRS 32
+#define DM_KEYS 64
+#define DM_PAD 8
+#define DM_LOG2E 1.4426950408889634f
+
+// a score in units of log 2: raw * scale, capped when a cap is given.  tanh(x) = 1 - 2 / (e^(2x) + 1): the absolute
+// error stays near 1e-7 for every x (large x: e^(2x) = inf, 2 / inf = 0).
+__device__ __forceinline__ float dm_score(float raw, float k_in, float k_out, bool capped) {
+  if (!capped) return raw * k_in;                           // k_in = scale * log2(e)
+  const float e = ts_exp2(raw * k_in);                      // k_in = 2 * log2(e) * scale / cap
+  return (1.0f - __fdividef(2.0f, e + 1.0f)) * k_out;       // k_out = cap * log2(e)
+}
+
+template <int D, int DV>
+__global__ void __launch_bounds__(128)
+diff_attention_mma_kernel(const bf16* __restrict__ q, bf16* __restrict__ out, const bf16* __restrict__ kv,
+                          const int* __restrict__ block_table, int max_blocks, const int* __restrict__ cu_tokens,
+                          const int* __restrict__ start_pos, int n_requests, int H, int G, int d, int vd, int page_size,
+                          DiffParams P, int window, int splits, float* __restrict__ part_o,
+                          float* __restrict__ part_ml, int page_shift, int single_tokens,
+                          const float* __restrict__ gate, long long ldg) {
+  pdl_launch_dependents();
+  pdl_wait();
+  constexpr int QP = D + DM_PAD, KP = 2 * D + DM_PAD, VP = DV + DM_PAD;   // row pitches in shared memory (bfloat16)
+  constexpr int FP = DV + 4;                                               // pitch of the float32 rows at the end
+  extern __shared__ __align__(16) unsigned char dm_raw[];
+  bf16* Qs = reinterpret_cast<bf16*>(dm_raw);               // [2 maps][32 pairs][QP]
+  bf16* Ks = Qs + 2 * DM_PAIRS * QP;                        // [2 stages][64][KP]: a key row is [map 1 (D) | map 2 (D)]
+  bf16* Vs = Ks + 2 * DM_KEYS * KP;                         // [2 stages][64][VP]
+  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31, gq = lane >> 2, tq = lane & 3;
+  const int map = warp >> 1;
+  const int gs = H / G, ntok = DM_PAIRS / gs;               // tokens of a tile
+  const int g = blockIdx.y, split = blockIdx.z;
+  const int d2 = 2 * d;
+  int r = 0, b = gridDim.x - 1 - blockIdx.x, len = 0;       // the grid's first CTAs take the last (longest) tiles
+  if (single_tokens) {
+    r = b;
+    b = 0;
+    len = 1;
+  } else {
+    for (; r < n_requests; r++) {
+      len = cu_tokens[r + 1] - cu_tokens[r];
+      const int tiles = (len + ntok - 1) / ntok;
+      if (b < tiles) break;
+      b -= tiles;
+    }
+  }
+  if (r >= n_requests) return;
+  const int tok0 = b * ntok, toks = min(ntok, len - tok0);
+  const int t0 = cu_tokens[r] + tok0, pos0 = start_pos[r] + tok0;
+  const int* bt = block_table + (size_t)r * max_blocks;
+  const int key_first = (window > 0 && pos0 - window + 1 > 0) ? pos0 - window + 1 : 0;
+  const int key_last = pos0 + toks - 1;
+  const int tile_lo = key_first / DM_KEYS, n_tiles_all = key_last / DM_KEYS - tile_lo + 1;
+  const int kt_begin = tile_lo + (int)((long long)n_tiles_all * split / splits);
+  const int kt_end = tile_lo + (int)((long long)n_tiles_all * (split + 1) / splits);
+  const size_t page_elems = (size_t)G * page_size * (d2 + vd);
+  const size_t k_head = (size_t)g * page_size * d2, v_head = (size_t)G * page_size * d2 + (size_t)g * page_size * vd;
+
+  auto page_of = [&](int kidx, int& off) {
+    if (page_shift >= 0) { off = kidx & (page_size - 1); return bt[kidx >> page_shift]; }
+    const int lp = kidx / page_size;
+    off = kidx - lp * page_size;
+    return bt[lp];
+  };
+  auto fetch = [&](int kt, int stage) {
+    bf16* ks = Ks + (size_t)stage * DM_KEYS * KP;
+    bf16* vs = Vs + (size_t)stage * DM_KEYS * VP;
+    for (int c = tid; c < DM_KEYS * (2 * D / 8); c += 128) {
+      const int key = c / (2 * D / 8), pc = (c - key * (2 * D / 8)) * 8, kidx = kt * DM_KEYS + key;
+      const int mp = pc >= D, col = pc - mp * D;            // padded column pc = map mp's column col
+      int page = -1, off = 0;
+      if (kidx >= key_first && kidx <= key_last && col < d) page = page_of(kidx, off);
+      const bf16* src = page >= 0 ? kv + (size_t)page * page_elems + k_head + (size_t)off * d2 + mp * d + col : kv;
+      ts_cp_async16(ks + key * KP + pc, src, page >= 0 ? 16 : 0);
+    }
+    for (int c = tid; c < DM_KEYS * (DV / 8); c += 128) {
+      const int key = c / (DV / 8), col = (c - key * (DV / 8)) * 8, kidx = kt * DM_KEYS + key;
+      int page = -1, off = 0;
+      if (kidx >= key_first && kidx <= key_last && col < vd) page = page_of(kidx, off);
+      const bf16* src = page >= 0 ? kv + (size_t)page * page_elems + v_head + (size_t)off * vd + col : kv;
+      ts_cp_async16(vs + key * VP + col, src, page >= 0 ? 16 : 0);
+    }
+  };
+
+  if (kt_begin < kt_end) fetch(kt_begin, 0);
+  ts_commit();
+  // the tile's queries: row = map * 32 + pair, pair = token * gs + head within the group; the rest is zero
+  for (int c = tid; c < 2 * DM_PAIRS * (D / 8); c += 128) {
+    const int row = c / (D / 8), col = (c - row * (D / 8)) * 8;
+    const int mp = row / DM_PAIRS, pr = row - mp * DM_PAIRS;
+    const int tk = pr / gs, hh = pr - tk * gs;
+    uint4 v = make_uint4(0, 0, 0, 0);
+    if (tk < toks && col < d)
+      v = *reinterpret_cast<const uint4*>(q + (size_t)(t0 + tk) * H * d2 + (size_t)(g * gs + hh) * d2 + mp * d + col);
+    *reinterpret_cast<uint4*>(Qs + row * QP + col) = v;
+  }
+  __syncthreads();
+  unsigned qa[D / 16][4];
+  {
+    const bf16* q0 = Qs + (warp * 16 + gq) * QP + 2 * tq;
+#pragma unroll
+    for (int ks = 0; ks < D / 16; ks++) {
+      qa[ks][0] = *reinterpret_cast<const unsigned*>(q0 + ks * 16);
+      qa[ks][1] = *reinterpret_cast<const unsigned*>(q0 + ks * 16 + 8 * QP);
+      qa[ks][2] = *reinterpret_cast<const unsigned*>(q0 + ks * 16 + 8);
+      qa[ks][3] = *reinterpret_cast<const unsigned*>(q0 + ks * 16 + 8 * QP + 8);
+    }
+  }
+  // this thread's two rows are the pairs pr0 and pr0 + 8 of its warp's map
+  const int pr0 = (warp & 1) * 16 + gq, pr1 = pr0 + 8;
+  const int tk0 = pr0 / gs, tk1 = pr1 / gs;
+  const bool live0 = tk0 < toks, live1 = tk1 < toks;
+  const bool warp_live = (warp & 1) * 16 < toks * gs;
+  const int p0 = pos0 + tk0, p1 = pos0 + tk1;
+  const int lo0 = (window > 0 && p0 - window + 1 > 0) ? p0 - window + 1 : 0;
+  const int lo1 = (window > 0 && p1 - window + 1 > 0) ? p1 - window + 1 : 0;
+  const bool capped = P.cap > 0.f;
+  const float k_in = capped ? 2.0f * DM_LOG2E * P.scale / P.cap : P.scale * DM_LOG2E;
+  const float k_out = P.cap * DM_LOG2E;
+  float m0 = -INFINITY, m1 = -INFINITY, l0 = 0.f, l1 = 0.f;
+  float o[DV / 8][4];
+#pragma unroll
+  for (int n = 0; n < DV / 8; n++) o[n][0] = o[n][1] = o[n][2] = o[n][3] = 0.f;
+
+  for (int kt = kt_begin; kt < kt_end; kt++) {
+    const int stage = (kt - kt_begin) & 1;
+    if (kt + 1 < kt_end) fetch(kt + 1, stage ^ 1);
+    ts_commit();
+    ts_wait<1>();
+    __syncthreads();
+    if (!warp_live) { __syncthreads(); continue; }          // this warp's 16 rows hold no token: it only fetches
+    const bf16* ks_ = Ks + (size_t)stage * DM_KEYS * KP + map * D;
+    const bf16* vs_ = Vs + (size_t)stage * DM_KEYS * VP;
+    float s[DM_KEYS / 8][4];
+#pragma unroll
+    for (int n = 0; n < DM_KEYS / 8; n++) s[n][0] = s[n][1] = s[n][2] = s[n][3] = 0.f;
+#pragma unroll
+    for (int ks = 0; ks < D / 16; ks += 2) {
+      unsigned kb[DM_KEYS / 8][4];
+#pragma unroll
+      for (int n = 0; n < DM_KEYS / 8; n++)
+        ts_ldmatrix_x4(kb[n], ks_ + (n * 8 + (lane & 7)) * KP + (lane >> 3) * 8 + ks * 16);
+#pragma unroll
+      for (int n = 0; n < DM_KEYS / 8; n++) ts_mma(s[n], qa[ks], kb[n][0], kb[n][1]);
+#pragma unroll
+      for (int n = 0; n < DM_KEYS / 8; n++) ts_mma(s[n], qa[ks + 1], kb[n][2], kb[n][3]);
+    }
+    float mx0 = -INFINITY, mx1 = -INFINITY;
+#pragma unroll
+    for (int n = 0; n < DM_KEYS / 8; n++) {
+      const int k0 = kt * DM_KEYS + n * 8 + 2 * tq, k1 = k0 + 1;
+      s[n][0] = (live0 && k0 <= p0 && k0 >= lo0) ? dm_score(s[n][0], k_in, k_out, capped) : -INFINITY;
+      s[n][1] = (live0 && k1 <= p0 && k1 >= lo0) ? dm_score(s[n][1], k_in, k_out, capped) : -INFINITY;
+      s[n][2] = (live1 && k0 <= p1 && k0 >= lo1) ? dm_score(s[n][2], k_in, k_out, capped) : -INFINITY;
+      s[n][3] = (live1 && k1 <= p1 && k1 >= lo1) ? dm_score(s[n][3], k_in, k_out, capped) : -INFINITY;
+      mx0 = fmaxf(mx0, fmaxf(s[n][0], s[n][1]));
+      mx1 = fmaxf(mx1, fmaxf(s[n][2], s[n][3]));
+    }
+    const float mn0 = fmaxf(m0, ts_quad_max(mx0)), mn1 = fmaxf(m1, ts_quad_max(mx1));
+    const float u0 = mn0 == -INFINITY ? 0.f : mn0, u1 = mn1 == -INFINITY ? 0.f : mn1;   // a row with no key yet
+    const float c0 = ts_exp2(m0 - u0), c1 = ts_exp2(m1 - u1);
+    m0 = mn0; m1 = mn1;
+    l0 *= c0; l1 *= c1;
+#pragma unroll
+    for (int n = 0; n < DV / 8; n++) { o[n][0] *= c0; o[n][1] *= c0; o[n][2] *= c1; o[n][3] *= c1; }
+#pragma unroll
+    for (int n = 0; n < DM_KEYS / 8; n++) {
+      s[n][0] = ts_exp2(s[n][0] - u0); s[n][1] = ts_exp2(s[n][1] - u0);
+      s[n][2] = ts_exp2(s[n][2] - u1); s[n][3] = ts_exp2(s[n][3] - u1);
+      l0 += s[n][0] + s[n][1];
+      l1 += s[n][2] + s[n][3];
+    }
+#pragma unroll
+    for (int j = 0; j < DM_KEYS / 16; j++) {
+      unsigned ah[4], al[4];
+      ts_split(s[2 * j][0], s[2 * j][1], ah[0], al[0]);
+      ts_split(s[2 * j][2], s[2 * j][3], ah[1], al[1]);
+      ts_split(s[2 * j + 1][0], s[2 * j + 1][1], ah[2], al[2]);
+      ts_split(s[2 * j + 1][2], s[2 * j + 1][3], ah[3], al[3]);
+#pragma unroll
+      for (int n2 = 0; n2 < DV / 16; n2 += 2) {
+        unsigned va[4], vb[4];
+        ts_ldmatrix_x4_trans(va, vs_ + (j * 16 + (lane & 15)) * VP + n2 * 16 + (lane >> 4) * 8);
+        ts_ldmatrix_x4_trans(vb, vs_ + (j * 16 + (lane & 15)) * VP + (n2 + 1) * 16 + (lane >> 4) * 8);
+        ts_mma(o[2 * n2], ah, va[0], va[1]);
+        ts_mma(o[2 * n2 + 1], ah, va[2], va[3]);
+        ts_mma(o[2 * n2 + 2], ah, vb[0], vb[1]);
+        ts_mma(o[2 * n2 + 3], ah, vb[2], vb[3]);
+        ts_mma(o[2 * n2], al, va[0], va[1]);
+        ts_mma(o[2 * n2 + 1], al, va[2], va[3]);
+        ts_mma(o[2 * n2 + 2], al, vb[0], vb[1]);
+        ts_mma(o[2 * n2 + 3], al, vb[2], vb[3]);
+      }
+    }
+    __syncthreads();          // all warps are done with this stage before the next fetch overwrites it
+  }
+  ts_wait<0>();
+  l0 = ts_quad_sum(l0);
+  l1 = ts_quad_sum(l1);
+  if (splits > 1) {
+#pragma unroll
+    for (int half = 0; half < 2; half++) {
+      if (!(half ? live1 : live0)) continue;
+      const int pr = half ? pr1 : pr0, tk = half ? tk1 : tk0;
+      const int h = g * gs + (pr - tk * gs), t = t0 + tk;
+      const size_t pi = (((size_t)t * H + h) * 2 + map) * splits + split;
+#pragma unroll
+      for (int n = 0; n < DV / 8; n++) {
+        const int col = n * 8 + 2 * tq;
+        if (col < vd) *reinterpret_cast<float2*>(part_o + pi * vd + col) = make_float2(o[n][2 * half], o[n][2 * half + 1]);
+      }
+      if (tq == 0) { part_ml[pi * 2] = half ? m1 : m0; part_ml[pi * 2 + 1] = half ? l1 : l0; }
+    }
+    return;
+  }
+  // one split: both maps of a pair meet in shared memory (the key and value stages are free now)
+  __syncthreads();
+  float* F = reinterpret_cast<float*>(Ks);                  // [2 maps][32 pairs][FP]
+#pragma unroll
+  for (int half = 0; half < 2; half++) {
+    if (!(half ? live1 : live0)) continue;
+    const int pr = half ? pr1 : pr0;
+    const float inv = 1.0f / (half ? l1 : l0);
+    float* fr = F + (size_t)(map * DM_PAIRS + pr) * FP;
+#pragma unroll
+    for (int n = 0; n < DV / 8; n++)
+      *reinterpret_cast<float2*>(fr + n * 8 + 2 * tq) = make_float2(o[n][2 * half] * inv, o[n][2 * half + 1] * inv);
+  }
+  __syncthreads();
+  for (int pr = warp; pr < toks * gs; pr += 4) {
+    const int tk = pr / gs, h = g * gs + (pr - tk * gs), t = t0 + tk;
+    const float* f1 = F + (size_t)pr * FP;
+    const float* f2 = F + (size_t)(DM_PAIRS + pr) * FP;
+    float a[DV / 32], ss = 0.f;
+#pragma unroll
+    for (int i = 0; i < DV / 32; i++) {
+      const int idx = lane + 32 * i;
+      a[i] = idx < vd ? f1[idx] - P.lambda * f2[idx] : 0.f;
+      ss = fmaf(a[i], a[i], ss);
+    }
+    ss = warp_sum(ss);
+    float f = P.out_scale / sqrtf(ss / (float)vd + P.eps);
+    if (gate) f /= 1.0f + expf(-gate[(size_t)t * ldg + h]);
+    bf16* orow = out + ((size_t)t * H + h) * vd;
+#pragma unroll
+    for (int i = 0; i < DV / 32; i++) {
+      const int idx = lane + 32 * i;
+      if (idx < vd) orow[idx] = __float2bfloat16_rn(a[i] * f);
+    }
+  }
+}
+
+// One warp per (token, head): the splits' (o, m, l) of both maps become the output row.  Lane s holds split s's maximum
+// and sum (up to 64 splits: two per lane); the output elements then add the splits' rows with weights that come by
+// shuffle.  vd <= 128.
+__global__ void __launch_bounds__(128)
+diff_combine_kernel(const float* __restrict__ part_o, const float* __restrict__ part_ml, bf16* __restrict__ out,
+                    int n_rows, int H, int vd, int splits, DiffParams P, const float* __restrict__ gate,
+                    long long ldg) {
+  pdl_launch_dependents();
+  pdl_wait();
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int row = blockIdx.x * 4 + warp;                    // t * H + h
+  if (row >= n_rows) return;
+  float a[2][4];
+#pragma unroll
+  for (int mp = 0; mp < 2; mp++) {
+    const size_t base = ((size_t)row * 2 + mp) * splits;
+    const float2* ml = reinterpret_cast<const float2*>(part_ml) + base;
+    const float2 x = lane < splits ? ml[lane] : make_float2(-INFINITY, 0.f);
+    const float2 y = lane + 32 < splits ? ml[lane + 32] : make_float2(-INFINITY, 0.f);
+    const float M = warp_max(fmaxf(x.x, y.x));
+    const float wx = x.x == -INFINITY ? 0.f : exp2f(x.x - M), wy = y.x == -INFINITY ? 0.f : exp2f(y.x - M);
+    const float inv = 1.0f / warp_sum(x.y * wx + y.y * wy);
+    const float* po = part_o + base * vd;
+#pragma unroll
+    for (int i = 0; i < 4; i++) {                           // every lane takes every turn: the shuffles need them all
+      const int idx = lane + 32 * i;
+      float acc = 0.f;
+      for (int s = 0; s < splits; s++) {
+        const float w = __shfl_sync(0xffffffffu, s < 32 ? wx : wy, s & 31);
+        if (idx < vd) acc = fmaf(po[(size_t)s * vd + idx], w, acc);
+      }
+      a[mp][i] = acc * inv;
+    }
+  }
+  float ss = 0.f;
+#pragma unroll
+  for (int i = 0; i < 4; i++) {
+    a[0][i] = lane + 32 * i < vd ? a[0][i] - P.lambda * a[1][i] : 0.f;
+    ss = fmaf(a[0][i], a[0][i], ss);
+  }
+  ss = warp_sum(ss);
+  float f = P.out_scale / sqrtf(ss / (float)vd + P.eps);
+  if (gate) f /= 1.0f + expf(-gate[(size_t)(row / H) * ldg + row % H]);
+#pragma unroll
+  for (int i = 0; i < 4; i++) {
+    const int idx = lane + 32 * i;
+    if (idx < vd) out[(size_t)row * vd + idx] = __float2bfloat16_rn(a[0][i] * f);
+  }
+}
+
+// q [n_tokens, H * 2d] and out [n_tokens, H * vd] bfloat16, dense; cu_tokens [n_requests + 1] rows of q / out per
+// request, start_pos [n_requests] the position of each request's first row; block_table [n_requests, max_blocks].
+// tiles: an upper bound of the sum over requests of ceil(tokens / (32 / (H / G))).  part_o [n_tokens * H * 2 * splits,
+// vd] and part_ml [n_tokens * H * 2 * splits, 2] float32 when splits > 1.  gate as in the generic kernel.
+extern "C" int qd_diff_attention_mma(const void* q, void* out, const void* kv, const int* block_table, int max_blocks,
+                                     const int* cu_tokens, const int* start_pos, int n_requests, int n_tokens,
+                                     int tiles, int H, int G, int d, int vd, int page_size, float scale, float cap,
+                                     float lambda, float eps, float out_scale, int window, const float* gate,
+                                     long long ldg, int splits, float* part_o, float* part_ml, cudaStream_t stream) {
+  if (n_tokens <= 0 || n_requests <= 0) return 0;
+  if (G <= 0 || H % G || H / G > DM_PAIRS || d <= 0 || vd <= 0 || d > 128 || vd > 128 || d % 8 || vd % 8 ||
+      page_size <= 0 || splits < 1 || splits > 64 || G > 65535 || (splits > 1 && (!part_o || !part_ml)))
+    return QD_ERR_UNSUPPORTED;
+  const DiffParams P = {scale, cap, lambda, eps, out_scale};
+  int page_shift = -1;
+  if ((page_size & (page_size - 1)) == 0)
+    for (page_shift = 0; (1 << page_shift) < page_size; page_shift++) {}
+  const int single_tokens = n_tokens == n_requests;         // every request has at least one token
+  if (single_tokens) tiles = n_requests;
+  dim3 grid(tiles, G, splits);
+#define DM_GO(D_, DV_)                                                                                              \
+  do {                                                                                                              \
+    const size_t smem = ((size_t)2 * DM_PAIRS * (D_ + DM_PAD) + 2 * DM_KEYS * (2 * D_ + DM_PAD) +                   \
+                         2 * DM_KEYS * (DV_ + DM_PAD)) * 2;                                                         \
+    static bool raised = false;                                                                                     \
+    if (!raised) {                                                                                                  \
+      cudaFuncSetAttribute(diff_attention_mma_kernel<D_, DV_>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem); \
+      raised = true;                                                                                                \
+    }                                                                                                               \
+    qd_launch(diff_attention_mma_kernel<D_, DV_>, grid, dim3(128), smem, stream, (const bf16*)q, (bf16*)out,        \
+              (const bf16*)kv, block_table, max_blocks, cu_tokens, start_pos, n_requests, H, G, d, vd, page_size, P, \
+              window, splits, part_o, part_ml, page_shift, single_tokens, gate, ldg);                               \
+  } while (0)
+  if (d <= 64 && vd <= 64) DM_GO(64, 64);
+  else if (d <= 64) DM_GO(64, 128);
+  else if (vd <= 64) DM_GO(128, 64);
+  else DM_GO(128, 128);
+#undef DM_GO
+  if (splits > 1) {
+    const int rows = n_tokens * H;
+    qd_launch(diff_combine_kernel, dim3((rows + 3) / 4), dim3(128), 0, stream, (const float*)part_o,
+              (const float*)part_ml, (bf16*)out, rows, H, vd, splits, P, gate, ldg);
+  }
   return qd_last_error();
 }

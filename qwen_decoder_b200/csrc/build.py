@@ -55,7 +55,8 @@ HEADERS = ["common.cuh", "entry_points.h"]
 EXTRA_DEPS: Dict[str, List[str]] = {
     "decode_attention_noalloc": ["attention_flash.cu", "decode_attention_noalloc.h"],
     "gated_block": ["short_conv.cuh"],
-    "attention_diff": ["short_conv.cuh"],
+    "attention_diff": ["short_conv.cuh", "mma_sync.cuh"],
+    "attention_sink": ["mma_sync.cuh"],
 }
 
 _loaded: Dict[str, ctypes.CDLL] = {}

@@ -1052,12 +1052,74 @@ def diff_attention_generic(q: torch.Tensor, out: torch.Tensor, kv: torch.Tensor,
 DIFF_MAX_VDIM = 512
 
 
+DIFF_MMA_PAIRS = 32      # (token, head within the group) pairs of one tile of the tensor-core kernel (two rows each)
+DIFF_MMA = _os.environ.get("QD_DIFF_MMA", "1") != "0"      # 0: every dtype and size on the float32 kernel
+
+
+def diff_mma_supported(dtype: torch.dtype, H: int, G: int, d: int, vd: int) -> bool:
+    """What the tensor-core form of the differential attention takes: bfloat16, per-map key sizes and value sizes
+    that are multiples of 8 up to 128, groups of up to 32 query heads per key/value head; any page size."""
+    return (dtype == torch.bfloat16 and H % G == 0 and H // G <= DIFF_MMA_PAIRS and d % 8 == 0 and vd % 8 == 0
+            and 0 < d <= 128 and 0 < vd <= 128)
+
+
+def diff_attention_mma(q: torch.Tensor, out: torch.Tensor, kv: torch.Tensor, block_table: torch.Tensor,
+                       cu_tokens: torch.Tensor, start_pos: torch.Tensor, n_requests: int, n_tokens: int, H: int, G: int,
+                       d: int, vd: int, page_size: int, scale: float, cap: float, lam: float, eps: float,
+                       out_scale: float, window: int, gate: Optional[torch.Tensor], splits: int = 1) -> None:
+    """``diff_attention_generic`` on tensor cores for portions of ``n_requests`` requests (rows cu_tokens[r] ..
+    cu_tokens[r+1]-1 of q and out, at positions start_pos[r]..): a decoded token is a portion of one.  ``splits`` > 1
+    shares every tile's keys among that many CTAs (for steps of few tokens over long contexts); a second launch adds
+    their parts up."""
+    assert q.dtype == out.dtype == kv.dtype == torch.bfloat16 and q.shape[1] == H * 2 * d and out.shape[1] == H * vd
+    assert kv.numel() % (G * page_size * (2 * d + vd)) == 0
+    assert block_table.dtype == torch.int32 and block_table.dim() == 2 and block_table.shape[0] >= n_requests
+    assert cu_tokens.dtype == torch.int32 and start_pos.dtype == torch.int32
+    assert gate is None or (gate.dtype == torch.float32 and gate.shape[1] == H and gate.stride(1) == 1)
+    _contig(q, "q"); _contig(out, "out"); _contig(kv, "kv"); _contig(block_table, "block_table")
+    ntok = DIFF_MMA_PAIRS // (H // G)
+    tiles = n_tokens // ntok + n_requests            # at least sum over requests of ceil(tokens / ntok)
+    part_o = part_ml = None
+    if splits > 1:
+        rows = out.shape[0] * H * 2
+        part_o = torch.empty((rows * splits, vd), dtype=torch.float32, device=q.device)
+        part_ml = torch.empty((rows * splits, 2), dtype=torch.float32, device=q.device)
+    _check(library("attention_diff").qd_diff_attention_mma(
+        _ptr(q), _ptr(out), _ptr(kv), _ptr(block_table), _I(block_table.shape[1]), _ptr(cu_tokens), _ptr(start_pos),
+        _I(n_requests), _I(n_tokens), _I(tiles), _I(H), _I(G), _I(d), _I(vd), _I(page_size), _F(scale), _F(cap),
+        _F(lam), _F(eps), _F(out_scale), _I(window), _ptr(gate), _LL(gate.stride(0) if gate is not None else 0),
+        _I(splits), _ptr(part_o), _ptr(part_ml), _stream()), "diff_attention_mma")
+    if splits > 1:
+        _launch_count[0] += 1
+
+
+def diff_decode_splits(ctas_without_split: int, max_keys: int) -> int:
+    """CTAs per (token, KV head) of the tensor-core kernel for single tokens: as many as fill two CTAs on every
+    multiprocessor, none with fewer than one tile of 64 keys, at most 64."""
+    by_fill = max(1, 2 * sm_count() // max(1, ctas_without_split))
+    by_work = max(1, (max_keys + 63) // 64)
+    return max(1, min(by_fill, by_work, 64))
+
+
 def diff_attention(q: torch.Tensor, out: torch.Tensor, kv: torch.Tensor, ctx, group, H: int, G: int, d: int, vd: int,
                    scale: float, cap: float, lam: float, eps: float, out_scale: float, window: int,
                    gate: Optional[torch.Tensor]) -> None:
-    """Differential attention for the step ``ctx`` over the paged cache of ``group``: the kernel for these sizes."""
-    diff_attention_generic(q, out, kv, group.block_table, ctx.token_request, ctx.positions, H, G, d, vd,
-                           group.page_size, scale, cap, lam, eps, out_scale, window, gate)
+    """Differential attention for the step ``ctx`` over the paged cache of ``group``: the kernel for these sizes.
+    Single tokens (all of the step, or the first ``num_decode`` of a mixed one) share their keys among CTAs."""
+    if not (DIFF_MMA and diff_mma_supported(q.dtype, H, G, d, vd)):
+        diff_attention_generic(q, out, kv, group.block_table, ctx.token_request, ctx.positions, H, G, d, vd,
+                               group.page_size, scale, cap, lam, eps, out_scale, window, gate)
+        return
+    T = q.shape[0]
+    args = (H, G, d, vd, group.page_size, scale, cap, lam, eps, out_scale, window, gate)
+    nd = T if ctx.all_decode else getattr(ctx, "num_decode", 0)
+    if nd:
+        keys = ctx.max_context if ctx.all_decode else ctx.decode_max_context
+        splits = diff_decode_splits(nd * G, min(keys, window or keys))
+        diff_attention_mma(q, out, kv, group.block_table, ctx.cu_tokens, ctx.start_pos, nd, nd, *args, splits=splits)
+    if nd < T:
+        diff_attention_mma(q, out, kv, group.block_table[nd:], ctx.cu_tokens[nd:], ctx.start_pos[nd:],
+                           ctx.num_requests - nd, T - nd, *args)
 
 
 # ------------------------------------------------------------------ tanh norm, gated activations, token gate

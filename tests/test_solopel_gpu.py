@@ -237,7 +237,9 @@ def test_one_far_key_stands_out(kind, dtype, tmp_path):
     for k, tr in enumerate((trace_tools.whole(seqs), trace_tools.decode_tail(seqs, tail=24),
                             trace_tools.portions(seqs, sizes=(100, 2, 3, 64)))):
         got = trace_tools.run_inprocess(runner, tr, str(tmp_path / f"o{k}"))
-        trace_tools.compare(tr, got, want, TOL[dtype])
+        # bfloat16: where two keys nearly tie, the rounding of q and of the cached rows shifts weight between them;
+        # one row in a hundred may lie above the tolerance (a lost key would be above it many times over)
+        trace_tools.compare(tr, got, want, TOL[dtype], stray=0.01 if dtype == "bfloat16" else 0.0)
 
 
 def test_greedy_generation_through_the_engine(models):
@@ -267,3 +269,37 @@ def test_greedy_generation_through_the_engine(models):
     alone = [e16.generate([p], SamplingParams(max_new_tokens=new, ignore_eos=True))[0] for p in prompts[:4]]
     agree = sum(a == b for a, b in zip(together, alone))
     assert agree >= 3, (together, alone)       # a bfloat16 near-tie may flip one of them
+
+
+@pytest.mark.parametrize("H,G,d,vd,ps,cap,window", [
+    (8, 2, 128, 128, 16, 30.0, 0), (4, 4, 48, 96, 64, 50.0, 0), (6, 1, 64, 64, 24, 0.0, 0), (32, 1, 8, 16, 16, 2.0, 0),
+    (3, 3, 72, 40, 32, 5.0, 100), (16, 2, 32, 128, 16, 0.0, 0)])
+def test_tensor_core_attention_against_the_float32_kernel(H, G, d, vd, ps, cap, window):
+    """The differential attention kernel on tensor cores (prompt portions at any start, single tokens with their
+    keys shared among CTAs) against the one-warp-per-head float32 kernel, on the same scattered pages."""
+    from qwen_decoder_b200 import kernels
+    dev = torch.device("cuda:0")
+    g = torch.Generator().manual_seed(H * 1000 + d)
+    portions = [(0, 70), (100, 37), (500, 3), (64, 64), (31, 2)]          # (cached before, new tokens)
+    singles = [0, 62, 63, 64, 899]                                         # cached before a single new token
+    for reqs in (portions, [(c, 1) for c in singles]):
+        R, T = len(reqs), sum(n for _, n in reqs)
+        blocks = max((c + n + ps - 1) // ps for c, n in reqs)
+        perm = torch.randperm(R * blocks + 3, generator=g)[:R * blocks].to(torch.int32).reshape(R, blocks)
+        kv = (torch.randn((R * blocks + 3, G * ps * (2 * d + vd)), generator=g) * 0.7).to(torch.bfloat16).to(dev)
+        q = (torch.randn((T, H * 2 * d), generator=g) * 1.5).to(torch.bfloat16).to(dev)
+        gate = torch.randn((T, H + 3), generator=g).to(dev)[:, 1:H + 1]
+        cu = torch.tensor([0] + list(np.cumsum([n for _, n in reqs])), dtype=torch.int32, device=dev)
+        start = torch.tensor([c for c, _ in reqs], dtype=torch.int32, device=dev)
+        token_req = torch.tensor([r for r, (_, n) in enumerate(reqs) for _ in range(n)], dtype=torch.int32, device=dev)
+        pos = torch.tensor([c + i for c, n in reqs for i in range(n)], dtype=torch.int32, device=dev)
+        bt = perm.to(dev).contiguous()
+        args = (H, G, d, vd, ps, d ** -0.5, cap, 0.37, 1e-5, 0.7, window, gate)
+        want = torch.empty((T, H * vd), dtype=torch.bfloat16, device=dev)
+        kernels.diff_attention_generic(q, want, kv, bt, token_req, pos, *args)
+        for splits in ((1, 3, 64) if T == R else (1,)):
+            got = torch.full_like(want, float("nan"))
+            kernels.diff_attention_mma(q, got, kv, bt, cu, start, R, T, *args, splits=splits)
+            torch.cuda.synchronize()
+            err = (got.float() - want.float()).abs().max().item()
+            assert err <= 0.03 * want.float().abs().max().item(), (splits, err)
