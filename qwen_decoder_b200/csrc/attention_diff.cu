@@ -496,54 +496,49 @@ diff_attention_mma_kernel(const bf16* __restrict__ q, bf16* __restrict__ out, co
   }
 }
 
-// One warp per (token, head): the splits' (o, m, l) of both maps become the output row.  Lane s holds split s's maximum
-// and sum (up to 64 splits: two per lane); the output elements then add the splits' rows with weights that come by
-// shuffle.  vd <= 128.
+// One CTA of 128 threads per (token, head): the splits' (o, m, l) of both maps become the output row.  Warp m makes map
+// m's weights (lane s holds split s's maximum and sum; up to 64 splits, two per lane); thread i then adds element i of
+// all splits' rows, loads that do not depend on one another, and the block's sum of squares gives the unit norm.
+// vd <= 128.
 __global__ void __launch_bounds__(128)
 diff_combine_kernel(const float* __restrict__ part_o, const float* __restrict__ part_ml, bf16* __restrict__ out,
                     int n_rows, int H, int vd, int splits, DiffParams P, const float* __restrict__ gate,
                     long long ldg) {
   pdl_launch_dependents();
   pdl_wait();
-  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  const int row = blockIdx.x * 4 + warp;                    // t * H + h
-  if (row >= n_rows) return;
-  float a[2][4];
-#pragma unroll
-  for (int mp = 0; mp < 2; mp++) {
-    const size_t base = ((size_t)row * 2 + mp) * splits;
-    const float2* ml = reinterpret_cast<const float2*>(part_ml) + base;
+  __shared__ float wgt[2][64];
+  __shared__ float inv_l[2];
+  __shared__ float scratch[40];
+  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+  const int row = blockIdx.x;                               // t * H + h
+  const size_t base = (size_t)row * 2 * splits;
+  if (warp < 2) {
+    const float2* ml = reinterpret_cast<const float2*>(part_ml) + base + (size_t)warp * splits;
     const float2 x = lane < splits ? ml[lane] : make_float2(-INFINITY, 0.f);
     const float2 y = lane + 32 < splits ? ml[lane + 32] : make_float2(-INFINITY, 0.f);
     const float M = warp_max(fmaxf(x.x, y.x));
     const float wx = x.x == -INFINITY ? 0.f : exp2f(x.x - M), wy = y.x == -INFINITY ? 0.f : exp2f(y.x - M);
-    const float inv = 1.0f / warp_sum(x.y * wx + y.y * wy);
-    const float* po = part_o + base * vd;
-#pragma unroll
-    for (int i = 0; i < 4; i++) {                           // every lane takes every turn: the shuffles need them all
-      const int idx = lane + 32 * i;
-      float acc = 0.f;
-      for (int s = 0; s < splits; s++) {
-        const float w = __shfl_sync(0xffffffffu, s < 32 ? wx : wy, s & 31);
-        if (idx < vd) acc = fmaf(po[(size_t)s * vd + idx], w, acc);
-      }
-      a[mp][i] = acc * inv;
+    const float L = warp_sum(x.y * wx + y.y * wy);
+    wgt[warp][lane] = wx;
+    wgt[warp][lane + 32] = wy;
+    if (lane == 0) inv_l[warp] = 1.0f / L;
+  }
+  __syncthreads();
+  float a1 = 0.f, a2 = 0.f;
+  if (tid < vd) {
+    const float* p1 = part_o + base * vd + tid;
+    const float* p2 = p1 + (size_t)splits * vd;
+#pragma unroll 8
+    for (int s = 0; s < splits; s++) {
+      a1 = fmaf(p1[(size_t)s * vd], wgt[0][s], a1);
+      a2 = fmaf(p2[(size_t)s * vd], wgt[1][s], a2);
     }
   }
-  float ss = 0.f;
-#pragma unroll
-  for (int i = 0; i < 4; i++) {
-    a[0][i] = lane + 32 * i < vd ? a[0][i] - P.lambda * a[1][i] : 0.f;
-    ss = fmaf(a[0][i], a[0][i], ss);
-  }
-  ss = warp_sum(ss);
+  const float o = tid < vd ? a1 * inv_l[0] - P.lambda * (a2 * inv_l[1]) : 0.f;
+  const float ss = block_sum(o * o, scratch);
   float f = P.out_scale / sqrtf(ss / (float)vd + P.eps);
   if (gate) f /= 1.0f + expf(-gate[(size_t)(row / H) * ldg + row % H]);
-#pragma unroll
-  for (int i = 0; i < 4; i++) {
-    const int idx = lane + 32 * i;
-    if (idx < vd) out[(size_t)row * vd + idx] = __float2bfloat16_rn(a[0][i] * f);
-  }
+  if (tid < vd) out[(size_t)row * vd + tid] = __float2bfloat16_rn(o * f);
 }
 
 // q [n_tokens, H * 2d] and out [n_tokens, H * vd] bfloat16, dense; cu_tokens [n_requests + 1] rows of q / out per
@@ -586,7 +581,7 @@ extern "C" int qd_diff_attention_mma(const void* q, void* out, const void* kv, c
 #undef DM_GO
   if (splits > 1) {
     const int rows = n_tokens * H;
-    qd_launch(diff_combine_kernel, dim3((rows + 3) / 4), dim3(128), 0, stream, (const float*)part_o,
+    qd_launch(diff_combine_kernel, dim3(rows), dim3(128), 0, stream, (const float*)part_o,
               (const float*)part_ml, (bf16*)out, rows, H, vd, splits, P, gate, ldg);
   }
   return qd_last_error();
