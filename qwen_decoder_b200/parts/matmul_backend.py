@@ -38,10 +38,9 @@ def _bias_as(bias: torch.Tensor, dtype: torch.dtype) -> torch.Tensor:
 
 def _cublas(x, w, bias, out):
     if out.dtype == torch.float32:
-        y = torch.mm(x, w.t(), out_dtype=torch.float32)
+        torch.mm(x, w.t(), out_dtype=torch.float32, out=out)         # float32 sums straight into the caller's buffer
         if bias is not None:
-            y += bias
-        out.copy_(y)
+            out += bias
     elif bias is not None:
         torch.addmm(_bias_as(bias, out.dtype), x, w.t(), out=out)
     else:

@@ -59,6 +59,15 @@ SB = config(523, 72, 2e-6, 2, [
     (attn(2, 2, 24, 40, diff=0.1, conv=1, softcap=30.0), moe(7, 1, 36)),
 ], logit_scale=1.0)
 CONFIGS = {"A": SA, "B": SB}
+# sizes nearer a real small model's, for the tensor-core paths: whole 16-byte pieces everywhere, four query heads per
+# kv head, keys of 32 per map and values of 64, several tiles of tokens and of keys in one prompt, a loop of three
+# layers run three times that ends at the last layer, three taps in the layers and four in the attention
+SC = config(701, 256, 1e-6, 3, [
+    (attn(8, 2, 32, 64, diff=0.25, conv=4, softcap=25.0), dense(384)),
+    (latent(8, 32, 64, 96), moe(8, 2, 96, shared=128)),
+    (attn(4, 4, 64, 32, diff=0.4, conv=2, softcap=40.0), moe(6, 1, 128)),
+    (latent(4, 64, 32, 160, scale=0.11), dense(512)),
+], loop=(1, 4, 3), logit_scale=0.6)
 
 
 def one_layer(mix, mlp, vocab=200, width=64, eps=1e-5, taps=3, loop=None, logit_scale=0.8):

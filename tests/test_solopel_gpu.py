@@ -190,6 +190,29 @@ def test_long_decoding_and_first_tokens(models, dtype, tmp_path):
     trace_tools.compare(tr, got, want, TOL[dtype])
 
 
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_a_larger_model_every_way_of_cutting(dtype, tmp_path):
+    """Sizes that take the tensor-core kernels in bfloat16 (several tiles of tokens and keys, grouped heads, single
+    tokens whose keys are shared among CTAs), prompts of up to 700 tokens: whole, with decoded tails, in portions,
+    and as mixed batches in a pool of two of the longest."""
+    folder = sc.make_folder(sc.SC, str(tmp_path / "m"), seed=91, edit=edits(dtype))
+    cfg, w = sc.read_folder(folder)
+    rng = random.Random(19)
+    seqs = [[rng.randrange(cfg["vocab"]) for _ in range(n)] for n in (700, 129, 64, 333, 5)]
+    want = expected(cfg, w, seqs)
+    runner = make_runner(folder, dtype, 2 * held(seqs), page_size=64)
+    both = seqs + seqs[::-1]
+    keep = lambda r, p: p % 7 == 0 or p >= len(both[r]) - 40            # which rows are compared
+    for k, tr in enumerate((trace_tools.whole(seqs, keep=keep), trace_tools.decode_tail(seqs, tail=36, keep=keep),
+                            trace_tools.portions(seqs, sizes=(130, 2, 61, 3, 256), keep=keep),
+                            trace_tools.mixed(both, 2 * held(seqs), seed=4, max_live=4, keep=keep, prompt_frac=0.85,
+                                              portion_sizes=(2, 17, 64, 130)))):
+        got = trace_tools.run_inprocess(runner, tr, str(tmp_path / f"o{k}"))
+        trace_tools.compare(tr, got, (want + want[::-1]) if k == 3 else want, TOL[dtype],
+                            stray=0.01 if dtype == "bfloat16" else 0.0)
+    all_free(runner)
+
+
 # kind -> (mixer, the factor on the queries in float32 and in bfloat16)
 FAR = {
     "latent": (sc.latent(4, 16, 32, 32, scale=1.0), 6.0, 1.2),
