@@ -730,3 +730,63 @@ extern "C" int qd_latent_expand(const float* o_lat, const void* wuv, int w_dtype
     return QD_ERR_UNSUPPORTED;
   return qd_last_error();
 }
+
+// ---------------------------------------------------------------------------------- rows for the expanded form
+// For prompt portions the keys and values of all heads are expanded from the cached rows by one product, and an
+// ordinary attention kernel runs over them.  ``latent_gather`` lays the first r elements of every cached row of the
+// requests' contexts out densely, request by request with Lmax rows each (rows past a request's context are zero):
+//   out[(q * Lmax + j), :] = cache row j of request q,  j < start_pos[q] + tokens of q in this step
+// grid (Lmax, requests), 128 threads.
+template <typename T>
+__global__ void __launch_bounds__(128)
+latent_gather_kernel(const T* __restrict__ cache, const int* __restrict__ block_table, int max_blocks,
+                     const int* __restrict__ cu_tokens, const int* __restrict__ start_pos, int page_size, int W, int r,
+                     T* __restrict__ out, int Lmax) {
+  pdl_launch_dependents();
+  pdl_wait();
+  const int j = blockIdx.x, q = blockIdx.y;
+  const int len = start_pos[q] + cu_tokens[q + 1] - cu_tokens[q];
+  T* o = out + ((size_t)q * Lmax + j) * r;
+  if (j >= len) {
+    for (int i = threadIdx.x; i < r; i += blockDim.x) o[i] = from_float<T>(0.f);
+    return;
+  }
+  const int page = block_table[(size_t)q * max_blocks + j / page_size];
+  const T* src = cache + ((size_t)page * page_size + j % page_size) * W;
+  for (int i = threadIdx.x; i < r; i += blockDim.x) o[i] = src[i];
+}
+
+extern "C" int qd_latent_gather(const void* cache, int dtype, const int* block_table, int max_blocks,
+                                const int* cu_tokens, const int* start_pos, int n_requests, int page_size, int W, int r,
+                                void* out, int Lmax, cudaStream_t stream) {
+  if (n_requests <= 0 || Lmax <= 0) return 0;
+  if (n_requests > 65535 || r <= 0 || r > W || page_size <= 0) return QD_ERR_UNSUPPORTED;
+  dim3 grid(Lmax, n_requests);
+  if (dtype == QD_BF16)
+    qd_launch(latent_gather_kernel<bf16>, grid, dim3(128), 0, stream, (const bf16*)cache, block_table, max_blocks,
+              cu_tokens, start_pos, page_size, W, r, (bf16*)out, Lmax);
+  else if (dtype == QD_F32)
+    qd_launch(latent_gather_kernel<float>, grid, dim3(128), 0, stream, (const float*)cache, block_table, max_blocks,
+              cu_tokens, start_pos, page_size, W, r, (float*)out, Lmax);
+  else
+    return QD_ERR_UNSUPPORTED;
+  return qd_last_error();
+}
+
+// out[t, 0..N) = in[t, 0..N) rounded to bfloat16 (in float32, rows ldin apart; out dense).
+__global__ void __launch_bounds__(256)
+round_rows_kernel(const float* __restrict__ in, long long ldin, bf16* __restrict__ out, int N, size_t n) {
+  pdl_launch_dependents();
+  pdl_wait();
+  const size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+  if (i >= n) return;
+  const size_t t = i / N;
+  out[i] = __float2bfloat16_rn(in[t * ldin + (i - t * N)]);
+}
+
+extern "C" int qd_round_rows(const float* in, long long ldin, void* out, int T, int N, cudaStream_t stream) {
+  if (T <= 0 || N <= 0) return 0;
+  const size_t n = (size_t)T * N;
+  qd_launch(round_rows_kernel, dim3((unsigned)((n + 255) / 256)), dim3(256), 0, stream, in, ldin, (bf16*)out, N, n);
+  return qd_last_error();
+}

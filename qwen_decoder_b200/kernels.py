@@ -758,6 +758,27 @@ def latent_attend(qcat: torch.Tensor, cache: torch.Tensor, block_table: torch.Te
         _launch_count[0] += 1
 
 
+def latent_gather(cache: torch.Tensor, block_table: torch.Tensor, cu_tokens: torch.Tensor, start_pos: torch.Tensor,
+                  n_requests: int, r: int, out: torch.Tensor, Lmax: int) -> None:
+    """out[q * Lmax + j] = the first ``r`` elements of cached row j of request q, for every row of the request's context
+    (what it holds and this step's tokens); rows past it are zero.  ``cache`` [pages, page_size, W]."""
+    assert out.shape == (n_requests * Lmax, r) and out.dtype == cache.dtype and cache.dim() == 3
+    assert block_table.dtype == torch.int32 and block_table.dim() == 2 and block_table.shape[0] >= n_requests
+    _contig(cache, "cache"); _contig(block_table, "block_table"); _contig(out, "out")
+    _check(library("latent_attention").qd_latent_gather(
+        _ptr(cache), _I(dtype_code(cache.dtype)), _ptr(block_table), _I(block_table.shape[1]), _ptr(cu_tokens),
+        _ptr(start_pos), _I(n_requests), _I(cache.shape[1]), _I(cache.shape[2]), _I(r), _ptr(out), _I(Lmax), _stream()),
+        "latent_gather")
+
+
+def round_rows(x: torch.Tensor, out: torch.Tensor) -> None:
+    """out = x rounded to bfloat16; x float32 [T, N] (a column range of a wider buffer is fine), out dense."""
+    assert x.dtype == torch.float32 and out.dtype == torch.bfloat16 and x.shape == out.shape and x.stride(1) == 1
+    _contig(out, "out")
+    _check(library("latent_attention").qd_round_rows(_ptr(x), _LL(x.stride(0)), _ptr(out), _I(x.shape[0]),
+                                                     _I(x.shape[1]), _stream()), "round_rows")
+
+
 def latent_expand(o_lat: torch.Tensor, wuv: torch.Tensor, gate: Optional[torch.Tensor], out: torch.Tensor,
                   dv: int, pre: Optional[torch.Tensor] = None) -> None:
     """out[t, h * dv + i] = (Wuv_h o_lat[t, h])[i] * sigmoid(gate[t, h * dv + i]); gate float32 (a column slice of a

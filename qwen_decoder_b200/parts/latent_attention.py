@@ -22,6 +22,8 @@ from __future__ import annotations
 
 from typing import List, Optional
 
+import os
+
 import torch
 
 from .. import kernels
@@ -35,6 +37,12 @@ from .linear import Linear
 # From this many tokens on, the bfloat16 engine makes the per-head products with Wuk and Wuv as batched library
 # products (as the framework does for every product of many tokens); below, the kernels read the weights themselves.
 LIBRARY_TOKENS = 64
+# Portions of prompts of at least this many tokens (the longest of the step) take the expanded form in bfloat16: keys
+# and values of all heads are made from the cached rows of the requests' contexts by one product and an ordinary
+# attention kernel runs over them.  A (token, key) pair then costs dn + dv products per head instead of 2 r, and a
+# row of context one expansion: worth it from about twenty tokens per request.
+EXPAND_TOKENS = int(os.environ.get("QD_LATENT_EXPAND_TOKENS", "32"))
+EXPAND_MAX_BYTES = 4 << 30          # the expanded keys and values of a step; above it the absorbed form runs
 
 
 def _hi_lo(x: torch.Tensor) -> torch.Tensor:
@@ -109,6 +117,31 @@ class LatentAttention(Mixer):
         self.w_uk_twice = torch.cat((uk, uk), dim=1).contiguous() if dtype == torch.bfloat16 else None
         self.w_uv_twice = torch.cat((uv, uv), dim=1).contiguous() if dtype == torch.bfloat16 else None
         self._no_table = torch.zeros((1, 0), dtype=torch.float32, device=device)
+        # the expanded form's one matrix: a row of context -> [keys of all heads | values of all heads]
+        self.w_ukv = torch.cat((self.w_uk, self.w_uv), dim=0).contiguous() if self._can_expand(dtype) else None
+
+    def _can_expand(self, dtype) -> bool:
+        return (dtype == torch.bfloat16 and self.rope_dim == 0 and not self.output_gate and not self.window
+                and kernels.sink_mma_supported(dtype, self.num_heads, self.num_heads, self.nope_dim, self.v_dim))
+
+    def _attend_expanded(self, q: torch.Tensor, attn: torch.Tensor, ctx, cache: PagedCacheView, nd: int,
+                         lmax: int) -> None:
+        """Requests nd.. of the step (rows cu_tokens[nd].. of q and attn): gather their contexts' rows, expand keys
+        and values, attend with the tensor-core kernel for heads that each have their own keys (a page of one key:
+        [keys of all heads | values of all heads] is a row of the product)."""
+        H, dn, dv, r = self.num_heads, self.nope_dim, self.v_dim, self.kv_rank
+        R = ctx.num_requests - nd
+        T = q.shape[0]
+        qb = torch.empty((T, H * dn), dtype=torch.bfloat16, device=q.device)
+        kernels.round_rows(q, qb)
+        rows = torch.empty((R * lmax, r), dtype=torch.bfloat16, device=q.device)
+        kernels.latent_gather(cache.kv, cache.group.block_table[nd:], ctx.cu_tokens[nd:], ctx.start_pos[nd:], R, r,
+                              rows, lmax)
+        kv = torch.empty((R * lmax, H * (dn + dv)), dtype=torch.bfloat16, device=q.device)
+        matmul_backend.linear(rows, self.w_ukv, None, kv)
+        table = torch.arange(R * lmax, dtype=torch.int32, device=q.device).view(R, lmax)
+        kernels.sink_attention_mma(qb, attn, kv, table, ctx.cu_tokens[nd:], ctx.start_pos[nd:], R,
+                                   T - int(ctx.host_cu_tokens[nd]), H, H, dn, dv, 1, self.scale, 0, None)
 
     def forward(self, x: torch.Tensor, ctx, cache: PagedCacheView) -> torch.Tensor:
         T, H = x.shape[0], self.num_heads
@@ -121,24 +154,46 @@ class LatentAttention(Mixer):
         kernels.latent_prep(u, 0, qr, qw, r, dr, self.w_dq_norm, self.w_dkv_norm, self.eps, *rot, ctx.positions,
                             cache.group.slot_map, cq, cache.kv, cache.write)
         q = self.up_q.forward(cq, out_dtype=torch.float32) if qr else u[:, :qw]
-        qcat = torch.empty((T, H, r + dr), dtype=torch.float32, device=x.device)
-        library = x.dtype == torch.bfloat16 and T >= LIBRARY_TOKENS and matmul_backend.mode != "generic"
+        attn = torch.empty((T, H * dv), dtype=x.dtype, device=x.device)
+        # rows 0 .. Ta-1 take the absorbed form: all of them, or the single tokens of a step whose portions expand
+        Ta = T
+        if self.w_ukv is not None and not ctx.all_decode and ctx.max_portion >= EXPAND_TOKENS:
+            nd = getattr(ctx, "num_decode", 0)
+            lmax = max(s + c1 - c0 for s, c0, c1 in zip(ctx.host_start_pos[nd:], ctx.host_cu_tokens[nd:],
+                                                              ctx.host_cu_tokens[nd + 1:]))
+            if (ctx.num_requests - nd) * lmax * H * (dn + dv) * 2 <= EXPAND_MAX_BYTES:
+                self._attend_expanded(q, attn, ctx, cache, nd, lmax)
+                Ta = nd
+        if Ta:
+            self._attend_absorbed(q[:Ta], u[:Ta, qw + r + dr:] if self.output_gate else None, attn[:Ta], ctx, cache, Ta)
+        return self.out.forward_partial(attn)
+
+    def _attend_absorbed(self, q: torch.Tensor, gate, attn: torch.Tensor, ctx, cache: PagedCacheView, T: int) -> None:
+        """Rows 0 .. T-1 of the step: the queries take Wuk in, attention runs over the cached rows themselves, and
+        Wuv expands the result."""
+        H = self.num_heads
+        dn, dr, dv, r = self.nope_dim, self.rope_dim, self.v_dim, self.kv_rank
+        pos = self.position
+        rot = (pos.cos, pos.sin, pos.rotary_dim) if pos is not None else (self._no_table, self._no_table, 0)
+        x_dtype, dev = attn.dtype, attn.device
+        positions, token_request = ctx.positions[:T], ctx.token_request[:T]
+        qcat = torch.empty((T, H, r + dr), dtype=torch.float32, device=dev)
+        library = x_dtype == torch.bfloat16 and T >= LIBRARY_TOKENS and matmul_backend.mode != "generic"
         pre = None
         if library:
             qn = _hi_lo(q.view(T, H, dn + dr)[:, :, :dn])                                   # [H, T, 2 dn]
             pre = torch.bmm(qn, self.w_uk_twice, out_dtype=torch.float32)                   # [H, T, r]
             matmul_backend.counters["library"] += 1
-        kernels.latent_absorb(q, self.w_uk, qcat, H, dn, dr, r, *rot, ctx.positions, pre=pre)
-        o_lat = torch.empty((T, H, r), dtype=torch.float32, device=x.device)
+        kernels.latent_absorb(q, self.w_uk, qcat, H, dn, dr, r, *rot, positions, pre=pre)
+        o_lat = torch.empty((T, H, r), dtype=torch.float32, device=dev)
         window = self.window or 0
         groups = -(-H // 8)
-        splits = attend_splits(T * groups, min(ctx.max_context, window or ctx.max_context))
-        kernels.latent_attend(qcat, cache.kv, cache.group.block_table, ctx.token_request, ctx.positions, r, dr,
+        keys = ctx.max_context if T == ctx.num_tokens else ctx.decode_max_context
+        splits = attend_splits(T * groups, min(keys, window or keys))
+        kernels.latent_attend(qcat, cache.kv, cache.group.block_table, token_request, positions, r, dr,
                               cache.group.page_size, self.scale, window, splits, o_lat)
-        attn = torch.empty((T, H * dv), dtype=x.dtype, device=x.device)
         pre = None
         if library:
             pre = torch.bmm(_hi_lo(o_lat), self.w_uv_twice, out_dtype=torch.float32)        # [H, T, dv]
             matmul_backend.counters["library"] += 1
-        kernels.latent_expand(o_lat, self.w_uv, u[:, qw + r + dr:] if self.output_gate else None, attn, dv, pre=pre)
-        return self.out.forward_partial(attn)
+        kernels.latent_expand(o_lat, self.w_uv, gate, attn, dv, pre=pre)
