@@ -26,10 +26,11 @@
 template <typename TC>
 __global__ void __launch_bounds__(256)
 diff_conv_write_kernel(const float* __restrict__ u, long long ldu, int Cq, int Ck, int Cv, int taps,
-                       const float* __restrict__ w, const float* __restrict__ state, long long state_stride,
+                       const float* __restrict__ w, float* state, long long state_stride,
                        long long state_off, const int* __restrict__ token_req, const int* __restrict__ cu_tokens,
                        const int* __restrict__ slots, TC* __restrict__ q_out, TC* __restrict__ kv,
-                       const int* __restrict__ slot_map, int page_size, int G, int d2, int vd, int write_kv) {
+                       const int* __restrict__ slot_map, int page_size, int G, int d2, int vd, int write_kv,
+                       int advance) {
   pdl_launch_dependents();
   pdl_wait();
   const int C = Cq + Ck + Cv;
@@ -39,8 +40,10 @@ diff_conv_write_kernel(const float* __restrict__ u, long long ldu, int Cq, int C
   float y;
   if (taps > 0) {
     const int r = token_req[t];
-    const float* st = state ? state + (size_t)slots[r] * state_stride + state_off : nullptr;
+    float* st = state ? state + (size_t)slots[r] * state_stride + state_off : nullptr;
     y = short_conv_at(u, ldu, C, taps, w, st, cu_tokens[r], t, c);
+    // every request brings one token: this thread alone reads and writes channel c of its request's kept inputs
+    if (advance) short_conv_advance(u, ldu, C, taps, st, t, t + 1, c);
   } else {
     y = u[(size_t)t * ldu + c];
   }
@@ -83,17 +86,19 @@ extern "C" int qd_diff_conv_write(const float* u, long long ldu, int H, int G, i
   const int d2 = 2 * d, Cq = H * d2, Ck = G * d2, Cv = G * vd, C = Cq + Ck + Cv;
   if (taps < 0 || (taps > 1 && !state) || T > 65535 || n_requests > 65535 || page_size <= 0) return QD_ERR_UNSUPPORTED;
   dim3 grid((C + 255) / 256, T);
+  // single tokens (one per request): the convolution's own launch moves the kept inputs on
+  const int advance = write && taps > 1 && T == n_requests;
   if (dtype == QD_F32)
     qd_launch(diff_conv_write_kernel<float>, grid, dim3(256), 0, stream, u, ldu, Cq, Ck, Cv, taps, w,
-              (const float*)state, state_stride, state_off, token_req, cu_tokens, slots, (float*)q_out, (float*)kv,
-              slot_map, page_size, G, d2, vd, write);
+              state, state_stride, state_off, token_req, cu_tokens, slots, (float*)q_out, (float*)kv,
+              slot_map, page_size, G, d2, vd, write, advance);
   else if (dtype == QD_BF16)
     qd_launch(diff_conv_write_kernel<bf16>, grid, dim3(256), 0, stream, u, ldu, Cq, Ck, Cv, taps, w,
-              (const float*)state, state_stride, state_off, token_req, cu_tokens, slots, (bf16*)q_out, (bf16*)kv,
-              slot_map, page_size, G, d2, vd, write);
+              state, state_stride, state_off, token_req, cu_tokens, slots, (bf16*)q_out, (bf16*)kv,
+              slot_map, page_size, G, d2, vd, write, advance);
   else
     return QD_ERR_UNSUPPORTED;
-  if (write && taps > 1)
+  if (write && taps > 1 && !advance)
     qd_launch(diff_conv_state_kernel, dim3((C + 255) / 256, n_requests), dim3(256), 0, stream, u, ldu, C, taps, state,
               state_stride, state_off, cu_tokens, slots);
   return qd_last_error();

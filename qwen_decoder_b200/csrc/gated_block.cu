@@ -7,7 +7,8 @@
 //   short_conv       y[t, c] = (residual ? u[t, c] : 0) + sum_j w[c, j] * u[t - taps + 1 + j, c] per request; inputs
 //                    before the portion's first token come from the request's state row (the last taps - 1 inputs,
 //                    oldest first, float32), zeros at a sequence's start (a fresh state row is zero)
-//   short_conv_state moves every request's state row on by its portion, whatever the portion's length
+//   short_conv_state moves every request's state row on by its portion, whatever the portion's length (a step of single
+//                    tokens, one per request, needs no such launch: the convolution's own thread moves its channel on)
 //   concat_round     out[t] = [a[t] | b[t]] in the engine's dtype, from two float32 rows
 //   plain_act        out = act(z) element by element (the tanh form of gelu), from float32 sums
 #include "common.cuh"
@@ -173,18 +174,20 @@ extern "C" int qd_gated_add_norm(float* x, const void* delta, int delta_dtype, i
 template <typename TI, typename TO>
 __global__ void __launch_bounds__(256)
 short_conv_kernel(const TI* __restrict__ u, long long ldu, int C, int taps, const float* __restrict__ w,
-                  const float* __restrict__ state, long long state_stride, long long state_off,
+                  float* state, long long state_stride, long long state_off,
                   const int* __restrict__ token_req, const int* __restrict__ cu_tokens, const int* __restrict__ slots,
-                  TO* __restrict__ out, long long ldo, int residual) {
+                  TO* __restrict__ out, long long ldo, int residual, int advance) {
   pdl_launch_dependents();
   pdl_wait();
   const int c = blockIdx.x * blockDim.x + threadIdx.x, t = blockIdx.y;
   if (c >= C) return;
   const int r = token_req[t];
-  const float* st = state ? state + (size_t)slots[r] * state_stride + state_off : nullptr;
+  float* st = state ? state + (size_t)slots[r] * state_stride + state_off : nullptr;
   float y = short_conv_at(u, ldu, C, taps, w, st, cu_tokens[r], t, c);
   if (residual) y += to_float(u[(size_t)t * ldu + c]);
   out[(size_t)t * ldo + c] = from_float<TO>(y);
+  // every request brings one token: this thread alone reads and writes channel c of its request's kept inputs
+  if (advance) short_conv_advance(u, ldu, C, taps, st, t, t + 1, c);
 }
 
 // grid (ceil(C / 256), requests): one thread per (request, channel) moves the channel's taps - 1 kept inputs on.
@@ -211,16 +214,18 @@ extern "C" int qd_short_conv(const void* u, int in_dtype, long long ldu, int C, 
   if (taps < 1 || C <= 0 || T > 65535 * 64 || (taps > 1 && !state)) return QD_ERR_UNSUPPORTED;
   dim3 grid((C + 255) / 256, T);
   if (grid.y > 65535) return QD_ERR_UNSUPPORTED;
+  // single tokens (one per request): the convolution's own launch moves the kept inputs on
+  const int advance = update_state && taps > 1 && T == n_requests;
 #define SC_GO(TI, TO)                                                                                          \
-  qd_launch(short_conv_kernel<TI, TO>, grid, dim3(256), 0, stream, (const TI*)u, ldu, C, taps, w, (const float*)state, \
-            state_stride, state_off, token_req, cu_tokens, slots, (TO*)out, ldo, residual)
+  qd_launch(short_conv_kernel<TI, TO>, grid, dim3(256), 0, stream, (const TI*)u, ldu, C, taps, w, state,       \
+            state_stride, state_off, token_req, cu_tokens, slots, (TO*)out, ldo, residual, advance)
   if (in_dtype == QD_F32 && out_dtype == QD_F32) SC_GO(float, float);
   else if (in_dtype == QD_F32 && out_dtype == QD_BF16) SC_GO(float, bf16);
   else if (in_dtype == QD_BF16 && out_dtype == QD_BF16) SC_GO(bf16, bf16);
   else if (in_dtype == QD_BF16 && out_dtype == QD_F32) SC_GO(bf16, float);
   else return QD_ERR_UNSUPPORTED;
 #undef SC_GO
-  if (update_state && taps > 1) {
+  if (update_state && taps > 1 && !advance) {
     dim3 g2((C + 255) / 256, n_requests);
     if (in_dtype == QD_F32)
       qd_launch(short_conv_state_kernel<float>, g2, dim3(256), 0, stream, (const float*)u, ldu, C, taps, state,

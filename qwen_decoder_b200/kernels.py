@@ -809,7 +809,7 @@ def mamba_conv(u: torch.Tensor, x_off: int, C: int, taps: int, w: torch.Tensor, 
         _ptr(u), _LL(u.stride(0)), _I(x_off), _I(C), _I(taps), _ptr(w), _ptr(bias), _ptr(state), _LL(state.stride(0)),
         _LL(conv_off), _ptr(token_req), _ptr(cu_tokens), _ptr(slots), _ptr(xbc), _I(T), _I(n_requests),
         _I(1 if update_state else 0), _stream()), "mamba_conv")
-    if update_state and taps > 1:
+    if update_state and taps > 1 and u.shape[0] != n_requests:      # single tokens: the same launch moves the state on
         _launch_count[0] += 1
 
 
@@ -998,7 +998,7 @@ def short_conv(u: torch.Tensor, w: torch.Tensor, state: Optional[torch.Tensor], 
         _LL(state.stride(0) if state is not None else 0), _LL(state_off), _ptr(token_req), _ptr(cu_tokens), _ptr(slots),
         _ptr(out), _I(dtype_code(out.dtype)), _LL(out.stride(0)), _I(T), _I(n_requests), _I(1 if residual else 0),
         _I(1 if update_state else 0), _stream()), "short_conv")
-    if update_state and taps > 1:
+    if update_state and taps > 1 and u.shape[0] != n_requests:      # single tokens: the same launch moves the state on
         _launch_count[0] += 1
 
 
@@ -1047,7 +1047,7 @@ def diff_conv_write(u: torch.Tensor, H: int, G: int, d: int, vd: int, w: Optiona
         _LL(state.stride(0) if state is not None else 0), _LL(state_off), _ptr(token_req), _ptr(cu_tokens), _ptr(slots),
         _ptr(q_out), _ptr(kv), _I(dtype_code(kv.dtype)), _ptr(slot_map), _I(page_size), _I(T), _I(n_requests),
         _I(1 if write else 0), _stream()), "diff_conv_write")
-    if write and taps > 1:
+    if write and taps > 1 and T != n_requests:      # single tokens: the same launch moves the state on
         _launch_count[0] += 1
 
 
