@@ -118,3 +118,20 @@ def test_the_plain_statement_is_causal_and_uses_every_part():
         changed = dict(w)
         changed[name] = w[name] + 0.25
         assert not torch.allclose(ps.forward(cfg, changed, seq), base, atol=1e-9), name
+
+
+def test_the_benchmark_models_describe():
+    """``bench.py --micro solopel``: both sizes parse, unroll to eight layer runs beside a model of eight layers, and
+    keep a cache and a state row per run."""
+    import os
+    import sys
+    sys.path.insert(0, os.path.join(os.path.dirname(os.path.abspath(__file__)), ".."))
+    import bench
+    from qwen_decoder_b200.config import describe_model
+    for size in ("S", "M"):
+        solopel, other = bench.solopel_configs(size)
+        spec = describe_model(solopel)
+        runs = [e for e in spec.schedule if spec.layers[e.layer].block == "pre_norm_gated"]
+        assert len(runs) == 8 == len(describe_model(other).schedule)
+        assert sum(spec.layers[e.layer].block == "loop_input" for e in spec.schedule) == 2
+    assert len(bench.solopel_configs("S", layers=2)[0].layers) == 2
