@@ -326,3 +326,54 @@ def test_tensor_core_attention_against_the_float32_kernel(H, G, d, vd, ps, cap, 
             torch.cuda.synchronize()
             err = (got.float() - want.float()).abs().max().item()
             assert err <= 0.03 * want.float().abs().max().item(), (splits, err)
+
+
+def _drawn_config(rng, routed: bool):
+    """A model drawn at random near a small model's scale: three to six layers in any order, any loop."""
+    n = rng.randint(3, 6)
+    layers = []
+    for _ in range(n):
+        if rng.random() < 0.5:
+            mix = sc.latent(rng.choice([2, 4, 6, 8]), rng.choice([16, 32, 48, 64]), rng.choice([16, 32, 64, 96]),
+                            rng.choice([64, 96, 128, 192]))
+        else:
+            H = rng.choice([2, 4, 8])
+            G = rng.choice([g for g in (1, 2, 4, 8) if H % g == 0])
+            mix = sc.attn(H, G, rng.choice([16, 32, 48, 64]), rng.choice([32, 64, 96, 128]), diff=rng.choice([0.2, 0.3, 0.5]),
+                          conv=rng.choice([2, 3, 4]), softcap=rng.choice([30.0, 50.0, None]))
+        k = rng.random()
+        mlp = None if k < 0.1 else sc.dense(rng.choice([256, 320, 512])) if k < 0.4 or not routed else \
+            sc.moe(rng.choice([4, 8, 16]), rng.choice([1, 2]), rng.choice([64, 96]), shared=rng.choice([None, 96, 128]))
+        layers.append((mix, mlp))
+    loop = None
+    if rng.random() < 0.8:
+        a = rng.randint(0, n - 1)
+        loop = (a, rng.randint(a + 1, n), rng.randint(1, 3))
+    return sc.config(rng.choice([300, 640, 777, 1000]), rng.choice([128, 160, 224, 256, 320]), rng.choice([1e-6, 1e-5]),
+                     rng.choice([2, 3, 4]), layers, loop=loop, logit_scale=rng.choice([0.5, 1.0, 0.37]))
+
+
+@pytest.mark.parametrize("seed", range(6))
+def test_models_drawn_at_random(seed, tmp_path):
+    """Sizes, layer orders, loops and constants drawn at random, every way of cutting: float32 with routed experts
+    (random routers: the choice is checked), bfloat16 with dense feed-forwards in their place (deep in a random
+    model no router can be made safe from rounding)."""
+    for dtype in ("float32", "bfloat16"):
+        rng = random.Random(7000 + seed)
+        cfg = _drawn_config(rng, routed=dtype == "float32")
+        folder = sc.make_folder(cfg, str(tmp_path / dtype), seed=seed, edit=clear_lambda)
+        cfg, w = sc.read_folder(folder)
+        seqs = [[rng.randrange(cfg["vocab"]) for _ in range(n)] for n in (300, 70, 33, 150)]
+        both = seqs + seqs[::-1]
+        want = expected(cfg, w, seqs)
+        runner = make_runner(folder, dtype, 2 * held(seqs))
+        keep = lambda r, p: p % 5 == 0 or p >= len(both[r]) - 40
+        for k, (tr, wnt) in enumerate((
+                (trace_tools.whole(seqs, keep=keep), want), (trace_tools.decode_tail(seqs, tail=36, keep=keep), want),
+                (trace_tools.portions(seqs, sizes=(40, 2, 17, 3, 100), keep=keep), want),
+                (trace_tools.mixed(both, 2 * held(seqs), seed=seed, max_live=4, keep=keep, prompt_frac=0.8,
+                                   portion_sizes=(2, 9, 33, 70)), want + want[::-1]))):
+            got = trace_tools.run_inprocess(runner, tr, str(tmp_path / f"{dtype}{k}"))
+            trace_tools.compare(tr, got, wnt, TOL[dtype])
+        all_free(runner)
+        del runner
