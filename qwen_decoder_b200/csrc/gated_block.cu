@@ -1,7 +1,8 @@
 // Kernels of a pre-norm layer whose branches join through a gate, whose mixer reads its input through a short
 // causal convolution, and of a loop of layers that takes the embedding output in again:
 //
-//   gated_add_norm   x[s] += sigmoid(g[s]) * delta[s] (element by element; g float32 logits; delta in the engine's
+//   gated_add_norm   x[s] += sigmoid(g[s] + b) * delta[s] (element by element; g float32 logits, b a bias per channel
+//                    or none; delta in the engine's
 //                    dtype or float32 partial sums that are added up here), then optionally out[r] = x[s] /
 //                    sqrt(mean(x[s]^2) + eps) * w  with s = rows[r] (or r)                          float32 arithmetic
 //   short_conv       y[t, c] = (residual ? u[t, c] : 0) + sum_j w[c, j] * u[t - taps + 1 + j, c] per request; inputs
@@ -18,7 +19,8 @@
 template <typename TD, typename TO>
 __global__ void __launch_bounds__(256)
 gated_add_norm_kernel(float* __restrict__ x, const TD* __restrict__ delta, int n_parts, size_t part_stride,
-                      const float* __restrict__ gate, const float* __restrict__ w, TO* __restrict__ out,
+                      const float* __restrict__ gate, const float* __restrict__ gate_bias,
+                      const float* __restrict__ w, TO* __restrict__ out,
                       const int* __restrict__ rows, int D, float eps, int write_back) {
   pdl_launch_dependents();
   pdl_wait();
@@ -34,7 +36,7 @@ gated_add_norm_kernel(float* __restrict__ x, const TD* __restrict__ delta, int n
     if (delta) {
       float dsum = to_float(delta[s * D + i]);
       for (int p = 1; p < n_parts; p++) dsum += to_float(delta[p * part_stride + s * D + i]);
-      if (gate) dsum *= 1.0f / (1.0f + expf(-gate[s * D + i]));
+      if (gate) dsum *= 1.0f / (1.0f + expf(-(gate[s * D + i] + (gate_bias ? gate_bias[i] : 0.f))));
       a += dsum;
       if (write_back) xr[i] = a;
     }
@@ -52,7 +54,8 @@ gated_add_norm_kernel(float* __restrict__ x, const TD* __restrict__ delta, int n
 template <typename TD, typename TO, int VPT>
 __global__ void __launch_bounds__(1024)
 gated_add_norm_vec_kernel(float* __restrict__ x, const TD* __restrict__ delta, int n_parts, size_t part_stride,
-                          const float* __restrict__ gate, const float* __restrict__ w, TO* __restrict__ out,
+                          const float* __restrict__ gate, const float* __restrict__ gate_bias,
+                          const float* __restrict__ w, TO* __restrict__ out,
                           const int* __restrict__ rows, int D, float eps, int write_back) {
   pdl_launch_dependents();
   const int n4 = D >> 2;
@@ -90,7 +93,11 @@ gated_add_norm_vec_kernel(float* __restrict__ x, const TD* __restrict__ delta, i
           d = make_float4(__low2float(d0), __high2float(d0), __low2float(d1), __high2float(d1));
         }
         if (gate) {
-          const float4 g = reinterpret_cast<const float4*>(gate + s * D)[i4];
+          float4 g = reinterpret_cast<const float4*>(gate + s * D)[i4];
+          if (gate_bias) {
+            const float4 b = reinterpret_cast<const float4*>(gate_bias)[i4];
+            g.x += b.x; g.y += b.y; g.z += b.z; g.w += b.w;
+          }
           d.x *= 1.0f / (1.0f + expf(-g.x)); d.y *= 1.0f / (1.0f + expf(-g.y));
           d.z *= 1.0f / (1.0f + expf(-g.z)); d.w *= 1.0f / (1.0f + expf(-g.w));
         }
@@ -123,16 +130,19 @@ gated_add_norm_vec_kernel(float* __restrict__ x, const TD* __restrict__ delta, i
   }
 }
 
-// x float32 [T, D]; delta [T, D] (``delta_dtype``) or float32 [n_parts, T, D], or null; gate float32 [T, D] or null;
-// w float32 [D] or null (no norm: out is not written); rows int32 [n_rows] or null.
+// x float32 [T, D]; delta [T, D] (``delta_dtype``) or float32 [n_parts, T, D], or null; gate float32 [T, D] or null, with
+// gate_bias float32 [D] (or null) added to every row of it; w float32 [D] or null (no norm: out is not written); rows
+// int32 [n_rows] or null.
 extern "C" int qd_gated_add_norm(float* x, const void* delta, int delta_dtype, int n_parts, long long part_stride,
-                                 const float* gate, const float* w, void* out, int out_dtype, const int* rows,
+                                 const float* gate, const float* gate_bias, const float* w, void* out, int out_dtype,
+                                 const int* rows,
                                  int n_rows, int D, float eps, int write_back, cudaStream_t stream) {
   if (n_rows <= 0) return 0;
   if (delta && delta_dtype != QD_F32 && (delta_dtype != QD_BF16 || n_parts != 1)) return QD_ERR_UNSUPPORTED;
   if (w && out_dtype != QD_F32 && out_dtype != QD_BF16) return QD_ERR_UNSUPPORTED;
   const bool df = !delta || delta_dtype == QD_F32, of = !w || out_dtype == QD_F32;
-  const bool al = !(((uintptr_t)x | (uintptr_t)delta | (uintptr_t)gate | (uintptr_t)w | (uintptr_t)out) & 15);
+  const bool al = !(((uintptr_t)x | (uintptr_t)delta | (uintptr_t)gate | (uintptr_t)gate_bias | (uintptr_t)w |
+                    (uintptr_t)out) & 15);
   if (D % 4 == 0 && D <= 8192 && al) {
     const int n4 = D / 4;
     int threads = n4 <= 1024 ? ((n4 + 31) / 32) * 32 : 1024;
@@ -140,10 +150,10 @@ extern "C" int qd_gated_add_norm(float* x, const void* delta, int delta_dtype, i
   do {                                                                                                          \
     if (n4 <= 1024)                                                                                             \
       qd_launch(gated_add_norm_vec_kernel<TD, TO, 1>, dim3(n_rows), dim3(threads), 0, stream, x, (const TD*)delta, \
-                n_parts, (size_t)part_stride, gate, w, (TO*)out, rows, D, eps, write_back);                     \
+                n_parts, (size_t)part_stride, gate, gate_bias, w, (TO*)out, rows, D, eps, write_back);                     \
     else                                                                                                        \
       qd_launch(gated_add_norm_vec_kernel<TD, TO, 2>, dim3(n_rows), dim3(threads), 0, stream, x, (const TD*)delta, \
-                n_parts, (size_t)part_stride, gate, w, (TO*)out, rows, D, eps, write_back);                     \
+                n_parts, (size_t)part_stride, gate, gate_bias, w, (TO*)out, rows, D, eps, write_back);                     \
   } while (0)
     if (df && of) GA_VEC(float, float);
     else if (df) GA_VEC(float, bf16);
@@ -159,7 +169,7 @@ extern "C" int qd_gated_add_norm(float* x, const void* delta, int delta_dtype, i
     if (smem > 48 * 1024)                                                                                      \
       cudaFuncSetAttribute(gated_add_norm_kernel<TD, TO>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem); \
     qd_launch(gated_add_norm_kernel<TD, TO>, dim3(n_rows), dim3(256), smem, stream, x, (const TD*)delta, n_parts, \
-              (size_t)part_stride, gate, w, (TO*)out, rows, D, eps, write_back);                               \
+              (size_t)part_stride, gate, gate_bias, w, (TO*)out, rows, D, eps, write_back);                               \
   } while (0)
   if (df && of) GA_GO(float, float);
   else if (df) GA_GO(float, bf16);

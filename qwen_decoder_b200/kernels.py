@@ -953,8 +953,10 @@ def moe_combine(y: torch.Tensor, place: torch.Tensor, wt: Optional[torch.Tensor]
 # ------------------------------------------------------------------ gated branches, short convolutions
 def gated_add_norm(x: torch.Tensor, delta: Optional[torch.Tensor], gate: Optional[torch.Tensor],
                    weight: Optional[torch.Tensor] = None, out: Optional[torch.Tensor] = None, eps: float = 0.0,
-                   rows: Optional[torch.Tensor] = None, write_back: bool = True) -> None:
-    """x += sigmoid(gate) * delta, element by element (x float32 [T, D]; gate float32 logits [T, D] or None; delta
+                   rows: Optional[torch.Tensor] = None, write_back: bool = True,
+                   gate_bias: Optional[torch.Tensor] = None) -> None:
+    """x += sigmoid(gate + gate_bias) * delta, element by element (x float32 [T, D]; gate float32 logits [T, D] or None,
+    gate_bias float32 [D] or None; delta
     [T, D], or float32 partial sums [n, T, D]); with ``weight`` also out[r] = x[s] / sqrt(mean(x[s]^2) + eps) * weight,
     s = rows[r] (or r).  ``write_back`` False leaves x as it was (the norm still sees the sum)."""
     T, D = x.shape
@@ -970,6 +972,8 @@ def gated_add_norm(x: torch.Tensor, delta: Optional[torch.Tensor], gate: Optiona
         _contig(delta, "delta")
     if gate is not None:
         _contig(gate, "gate")
+    assert gate_bias is None or (gate is not None and gate_bias.dtype == torch.float32 and gate_bias.numel() == D
+                                 and gate_bias.is_contiguous())
     n_rows = T
     if weight is not None:
         n_rows = out.shape[0]
@@ -977,7 +981,8 @@ def gated_add_norm(x: torch.Tensor, delta: Optional[torch.Tensor], gate: Optiona
         assert rows is None or (rows.dtype == torch.int32 and rows.numel() == n_rows)
     _check(library("gated_block").qd_gated_add_norm(
         _ptr(x), _ptr(delta), _I(dtype_code(delta.dtype) if delta is not None else 0), _I(n_parts), _LL(T * D),
-        _ptr(gate), _ptr(weight), _ptr(out), _I(dtype_code(out.dtype) if out is not None else 0), _ptr(rows),
+        _ptr(gate), _ptr(gate_bias), _ptr(weight), _ptr(out), _I(dtype_code(out.dtype) if out is not None else 0),
+        _ptr(rows),
         _I(n_rows), _I(D), _F(eps), _I(1 if write_back else 0), _stream()), "gated_add_norm")
 
 

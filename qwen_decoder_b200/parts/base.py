@@ -60,17 +60,19 @@ class ResidualStream:
         self.delta_unit = None                              # (u, eps): the pending branch joins unit-normalised
         self.delta2: Optional[torch.Tensor] = None          # a second pending branch (plain)
         self.delta_gate: Optional[torch.Tensor] = None      # float32 logits [T, D]: the pending branch joins times their sigmoid
+        self.delta_gate_bias: Optional[torch.Tensor] = None  # float32 [D]: added to every row of the logits first
         self.origin: Optional[torch.Tensor] = None          # the embedding output, kept when a block reads it again
 
     def push(self, delta: torch.Tensor, scale: Optional[torch.Tensor] = None, unit=None,
-             gate: Optional[torch.Tensor] = None) -> None:
-        """Hand over a branch output (times ``scale`` along D, or times sigmoid(``gate``) element by element, if
-        given); what is still pending is added first."""
+             gate: Optional[torch.Tensor] = None, gate_bias: Optional[torch.Tensor] = None) -> None:
+        """Hand over a branch output (times ``scale`` along D, or times sigmoid(``gate`` + ``gate_bias``) element by
+        element, if given); what is still pending is added first."""
         self.flush()
         self.delta = delta
         self.delta_scale = scale
         self.delta_unit = unit
         self.delta_gate = gate
+        self.delta_gate_bias = gate_bias
 
     def push_pair(self, delta: torch.Tensor, delta2: torch.Tensor) -> None:
         """Hand over the outputs of two branches that read the same x."""
@@ -88,6 +90,7 @@ class ResidualStream:
 
     def clear(self) -> None:
         self.delta = self.delta_scale = self.delta_unit = self.delta2 = self.delta_gate = None
+        self.delta_gate_bias = None
 
     def settle(self, gated_ok: bool = False) -> None:
         """Add what only ``flush`` can add (a second output, a unit-normalised one, and -- unless the caller's own
@@ -101,7 +104,7 @@ class ResidualStream:
         if self.delta_gate is not None:
             if self.delta2 is not None or self.delta_unit is not None or self.delta_scale is not None:
                 raise ValueError("a gated branch beside a second, a scaled or a unit-normalised one is not supported")
-            kernels.gated_add_norm(self.x, self.delta, self.delta_gate)
+            kernels.gated_add_norm(self.x, self.delta, self.delta_gate, gate_bias=self.delta_gate_bias)
         elif self.delta2 is None and self.delta_unit is None:
             kernels.residual_add(self.x, self.delta, self.delta_scale)
         else:

@@ -274,6 +274,13 @@ class GatedPreNormBlock(Block):
             return cache.state
         return cache.paged                              # None for a mixer that caches nothing
 
+    @staticmethod
+    def _gate_logits(gate: Linear, h: torch.Tensor) -> torch.Tensor:
+        """W h as float32 sums; the bias waits with them and is added by the kernel that takes the sigmoid."""
+        g = torch.empty((h.shape[0], gate.out_features), dtype=torch.float32, device=h.device)
+        matmul_backend.linear(h, gate.weight, None, g)
+        return g
+
     def forward(self, stream: ResidualStream, ctx, cache) -> None:
         h = self.norm1.forward(stream, self.dtype)
         hm = h
@@ -283,12 +290,12 @@ class GatedPreNormBlock(Block):
             kernels.short_conv(h, self.conv_w, st.state if st is not None else None, self.state_off, ctx.token_request,
                                ctx.cu_tokens, ctx.state_slots, hm, ctx.num_requests, residual=True,
                                update_state=bool(st is not None and st.write))
-        g = self.gate1.forward(h, out_dtype=torch.float32)
-        stream.push(self.mixer.forward(hm, ctx, self._mixer_cache(cache)), gate=g)
+        g = self._gate_logits(self.gate1, h)
+        stream.push(self.mixer.forward(hm, ctx, self._mixer_cache(cache)), gate=g, gate_bias=self.gate1.bias)
         if self.feed_forward is not None:
             h = self.norm2.forward(stream, self.dtype)
-            g = self.gate2.forward(h, out_dtype=torch.float32)
-            stream.push(self.feed_forward.forward(h, ctx), gate=g)
+            g = self._gate_logits(self.gate2, h)
+            stream.push(self.feed_forward.forward(h, ctx), gate=g, gate_bias=self.gate2.bias)
 
 
 @register_part("block", "loop_input")

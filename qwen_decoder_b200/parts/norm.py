@@ -52,7 +52,7 @@ class RMSNorm(Norm):
         out = torch.empty((n, self.size), dtype=out_dtype, device=stream.x.device)
         if stream.delta_gate is not None:       # a branch that joins through a gate: added and normed in one launch
             kernels.gated_add_norm(stream.x, stream.delta, stream.delta_gate, self.weight, out, self.eps, rows=rows,
-                                   write_back=rows is None)
+                                   write_back=rows is None, gate_bias=stream.delta_gate_bias)
             if rows is None:
                 stream.clear()
             return out
