@@ -9,9 +9,10 @@ from . import qwen2 as _qwen2  # registers Qwen2ForCausalLM
 from .zunuvik import ZunuvikConfig  # registers Zunuvik
 from .veterax import VeteraxConfig  # registers Veterax
 from .solopel import SolopelConfig  # registers Solopel
+from .fogurax import FoguraxConfig  # registers Fogurax
 
 __all__ = [
-    "ConfigError", "Qwen2Config", "ZunuvikConfig", "VeteraxConfig", "SolopelConfig", "read_config_json", "write_config_json", "PART_KINDS",
+    "ConfigError", "Qwen2Config", "ZunuvikConfig", "VeteraxConfig", "SolopelConfig", "FoguraxConfig", "read_config_json", "write_config_json", "PART_KINDS",
     "config_from_dict", "create_part", "describe_model", "known_architectures", "load_config",
     "lookup_architecture", "register_architecture", "register_part", "unregister_architecture",
     "unregister_part", "LayerSpec", "ModelSpec", "PartSpec", "ScheduleEntry",

@@ -10,6 +10,12 @@
 //             arithmetic, any sizes; tiles of 32 keys counted from key 0, so the order of every sum depends on the
 //             token's position only
 //
+//
+// Further options of ``attend`` (``AttnExtra``): ``chunk`` > 0 lets a query see only the keys of its own block of
+// ``chunk`` positions (blocks counted from position 0 of the sequence); ``gate`` multiplies head h's output row by
+// sigmoid(gate[t * gate_ld + h]) (float32 logits); ``out_scale`` multiplies it by a constant; ``out_stride`` is the
+// distance between output rows, so that the heads may land in a column range of a wider tensor.
+//
 // A page of the cache holds the keys [G, page_size, d] and then the values [G, page_size, vd].
 #include "common.cuh"
 #include "mma_sync.cuh"
@@ -17,6 +23,27 @@
 
 #define AS_MAX_D 512
 #define AS_WARPS 4
+
+struct AttnExtra {
+  int chunk;              // 0: none
+  const float* gate;      // float32 logits, row t at t * gate_ld, head h at + h; null: none
+  long long gate_ld;
+  float out_scale;
+  long long out_stride;   // elements between output rows
+};
+
+// The first key a query at ``pos`` sees.
+__device__ __forceinline__ int as_key_lo(int pos, int window, int chunk) {
+  int lo = (window > 0 && pos - window + 1 > 0) ? pos - window + 1 : 0;
+  if (chunk > 0) { const int c = pos - pos % chunk; lo = c > lo ? c : lo; }
+  return lo;
+}
+// What the finished row of (token t, head h) is multiplied by.
+__device__ __forceinline__ float as_out_factor(const AttnExtra& ex, int t, int h) {
+  float f = ex.out_scale;
+  if (ex.gate) f *= 1.0f / (1.0f + expf(-ex.gate[(size_t)t * ex.gate_ld + h]));
+  return f;
+}
 
 __device__ __forceinline__ float as_ld(const void* p, int code, size_t i) {
   return code == QD_F32 ? reinterpret_cast<const float*>(p)[i] : __bfloat162float(reinterpret_cast<const bf16*>(p)[i]);
@@ -136,7 +163,7 @@ sink_attention_generic_kernel(const T* __restrict__ q, long long q_stride, T* __
                               const T* __restrict__ kv, const int* __restrict__ block_table, int max_blocks,
                               const int* __restrict__ token_req, const int* __restrict__ positions, int n_tokens,
                               int H, int G, int d, int vd, int page_size, float scale, int window,
-                              const float* __restrict__ sinks) {
+                              const float* __restrict__ sinks, AttnExtra ex) {
   pdl_launch_dependents();
   pdl_wait();
   extern __shared__ float smem[];
@@ -152,7 +179,7 @@ sink_attention_generic_kernel(const T* __restrict__ q, long long q_stride, T* __
 
   const int pos = positions[t];
   const int* bt = block_table + (size_t)token_req[t] * max_blocks;
-  const int key_lo = (window > 0 && pos - window + 1 > 0) ? pos - window + 1 : 0;
+  const int key_lo = as_key_lo(pos, window, ex.chunk);
   const size_t page_elems = (size_t)G * page_size * (d + vd);
   const size_t k_head = (size_t)g * page_size * d;
   const size_t v_head = (size_t)G * page_size * d + (size_t)g * page_size * vd;
@@ -203,7 +230,7 @@ sink_attention_generic_kernel(const T* __restrict__ q, long long q_stride, T* __
     for (int i = 0; i < AS_MAX_D / 32; i++) o[i] *= c;
   }
   T* orow = out + (size_t)t * out_stride + (size_t)h * vd;
-  const float inv = 1.0f / l;
+  const float inv = as_out_factor(ex, t, h) / l;
 #pragma unroll
   for (int i = 0; i < AS_MAX_D / 32; i++) {
     const int idx = lane + 32 * i;
@@ -217,6 +244,7 @@ extern "C" int qd_sink_attention_generic(const void* q, long long q_stride, void
                                          const void* kv, int dtype, const int* block_table, int max_blocks,
                                          const int* token_req, const int* positions, int n_tokens, int H, int G, int d,
                                          int vd, int page_size, float scale, int window, const float* sinks,
+                                         int chunk, const float* gate, long long gate_ld, float out_scale,
                                          cudaStream_t stream) {
   if (n_tokens <= 0) return 0;
   if (d <= 0 || d > AS_MAX_D || vd <= 0 || vd > AS_MAX_D || G <= 0 || H % G != 0 || page_size <= 0)
@@ -224,14 +252,15 @@ extern "C" int qd_sink_attention_generic(const void* q, long long q_stride, void
   const long long items = (long long)n_tokens * H;
   const unsigned blocks = (unsigned)((items + AS_WARPS - 1) / AS_WARPS);
   const size_t smem = (size_t)AS_WARPS * d * sizeof(float);
+  const AttnExtra ex = {chunk, gate, gate_ld, out_scale, out_stride};
   if (dtype == QD_F32)
     qd_launch(sink_attention_generic_kernel<float>, dim3(blocks), dim3(AS_WARPS * 32), smem, stream, (const float*)q,
               q_stride, (float*)out, out_stride, (const float*)kv, block_table, max_blocks, token_req, positions,
-              n_tokens, H, G, d, vd, page_size, scale, window, sinks);
+              n_tokens, H, G, d, vd, page_size, scale, window, sinks, ex);
   else if (dtype == QD_BF16)
     qd_launch(sink_attention_generic_kernel<bf16>, dim3(blocks), dim3(AS_WARPS * 32), smem, stream, (const bf16*)q,
               q_stride, (bf16*)out, out_stride, (const bf16*)kv, block_table, max_blocks, token_req, positions,
-              n_tokens, H, G, d, vd, page_size, scale, window, sinks);
+              n_tokens, H, G, d, vd, page_size, scale, window, sinks, ex);
   else
     return QD_ERR_UNSUPPORTED;
   return qd_last_error();
@@ -259,7 +288,7 @@ sink_attention_mma_kernel(const bf16* __restrict__ q, bf16* __restrict__ out, co
                           const int* __restrict__ start_pos, int n_requests, int H, int G, int d, int vd, int page_size,
                           float scale_log2, int window, const float* __restrict__ sinks, int splits,
                           float* __restrict__ part_o, float* __restrict__ part_ml, int page_shift,
-                          unsigned* __restrict__ tickets, int single_tokens) {
+                          unsigned* __restrict__ tickets, int single_tokens, AttnExtra ex) {
   pdl_launch_dependents();
   pdl_wait();
   constexpr int KP = D + TS_PAD, VP = DV + TS_PAD;          // row pitches in shared memory (bfloat16)
@@ -289,7 +318,7 @@ sink_attention_mma_kernel(const bf16* __restrict__ q, bf16* __restrict__ out, co
   const int tok0 = b * ntok, toks = min(ntok, len - tok0);  // tokens tok0 .. tok0 + toks - 1 of the request's portion
   const int t0 = cu_tokens[r] + tok0, pos0 = start_pos[r] + tok0;
   const int* bt = block_table + (size_t)r * max_blocks;
-  const int key_first = (window > 0 && pos0 - window + 1 > 0) ? pos0 - window + 1 : 0;
+  const int key_first = as_key_lo(pos0, window, ex.chunk);   // the tile's first token sees the earliest key
   const int key_last = pos0 + toks - 1;
   const int tile_lo = key_first / TS_KEYS, n_tiles_all = key_last / TS_KEYS - tile_lo + 1;
   const int kt_begin = tile_lo + (int)((long long)n_tiles_all * split / splits);
@@ -352,8 +381,7 @@ sink_attention_mma_kernel(const bf16* __restrict__ q, bf16* __restrict__ out, co
   const bool live0 = tk0 < toks, live1 = tk1 < toks;
   const bool warp_live = warp * 16 < toks * gs;
   const int p0 = pos0 + tk0, p1 = pos0 + tk1;
-  const int lo0 = (window > 0 && p0 - window + 1 > 0) ? p0 - window + 1 : 0;
-  const int lo1 = (window > 0 && p1 - window + 1 > 0) ? p1 - window + 1 : 0;
+  const int lo0 = as_key_lo(p0, window, ex.chunk), lo1 = as_key_lo(p1, window, ex.chunk);
   float m0 = -INFINITY, m1 = -INFINITY, l0 = 0.f, l1 = 0.f;
   float o[DV / 8][4];
 #pragma unroll
@@ -461,12 +489,12 @@ sink_attention_mma_kernel(const bf16* __restrict__ q, bf16* __restrict__ out, co
       c = exp2f(m - mn);
       l = l * c + exp2f(sk - mn);
     }
-    const float f = c / l;
+    const float f = c / l * as_out_factor(ex, t, h);
 #pragma unroll
     for (int n = 0; n < DV / 8; n++) {
       const int col = n * 8 + 2 * tq;
       if (col < vd)
-        *reinterpret_cast<unsigned*>(out + (size_t)t * H * vd + (size_t)h * vd + col) =
+        *reinterpret_cast<unsigned*>(out + (size_t)t * ex.out_stride + (size_t)h * vd + col) =
             ts_pack(o[n][2 * half] * f, o[n][2 * half + 1] * f);
     }
   }
@@ -513,7 +541,7 @@ sink_attention_mma_kernel(const bf16* __restrict__ q, bf16* __restrict__ out, co
       L += sums[tid * splits + s2] * w;
       wgt[tid * splits + s2] = w;
     }
-    inv_l[tid] = 1.0f / L;
+    inv_l[tid] = as_out_factor(ex, t0 + tk_, h) / L;
   }
   __syncthreads();
   const int vd2 = vd >> 1;                                  // two elements per thread and turn
@@ -530,7 +558,7 @@ sink_attention_mma_kernel(const bf16* __restrict__ q, bf16* __restrict__ out, co
       ay = fmaf(v.y, w, ay);
     }
     const float f = inv_l[row];
-    *reinterpret_cast<unsigned*>(out + (size_t)(t0 + tk_) * H * vd + (size_t)h * vd + i) = ts_pack(ax * f, ay * f);
+    *reinterpret_cast<unsigned*>(out + (size_t)(t0 + tk_) * ex.out_stride + (size_t)h * vd + i) = ts_pack(ax * f, ay * f);
   }
 }
 
@@ -539,7 +567,7 @@ sink_attention_mma_kernel(const bf16* __restrict__ q, bf16* __restrict__ out, co
 // come by shuffle, so the loads of all splits are independent of one another.
 __global__ void __launch_bounds__(128)
 sink_combine_kernel(const float* __restrict__ part_o, const float* __restrict__ part_ml, const float* __restrict__ sinks,
-                    bf16* __restrict__ out, int n_rows, int H, int vd, int splits) {
+                    bf16* __restrict__ out, int n_rows, int H, int vd, int splits, AttnExtra ex) {
   pdl_launch_dependents();
   pdl_wait();
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -552,7 +580,8 @@ sink_combine_kernel(const float* __restrict__ part_o, const float* __restrict__ 
   const float M = fmaxf(warp_max(fmaxf(a.x, b.x)), sk);
   const float wa = a.x == -INFINITY ? 0.f : exp2f(a.x - M), wb = b.x == -INFINITY ? 0.f : exp2f(b.x - M);
   const float L = warp_sum(a.y * wa + b.y * wb) + (sinks ? exp2f(sk - M) : 0.f);
-  const float inv = 1.0f / L;
+  const int t_ = row / H, h_ = row - t_ * H;
+  const float inv = as_out_factor(ex, t_, h_) / L;
   const float* po = part_o + (size_t)row * splits * vd;
   for (int i0 = 0; i0 < vd; i0 += 32) {                     // every lane takes every turn: the shuffles need them all
     const int i = i0 + lane;
@@ -562,7 +591,7 @@ sink_combine_kernel(const float* __restrict__ part_o, const float* __restrict__ 
       const float w = __shfl_sync(0xffffffffu, s < 32 ? wa : wb, s & 31);
       if (i < vd) acc = fmaf(po[(size_t)s * vd + i], w, acc);
     }
-    if (i < vd) out[(size_t)row * vd + i] = __float2bfloat16_rn(acc * inv);
+    if (i < vd) out[(size_t)t_ * ex.out_stride + (size_t)h_ * vd + i] = __float2bfloat16_rn(acc * inv);
   }
 }
 
@@ -575,11 +604,14 @@ extern "C" int qd_sink_attention_mma(const void* q, void* out, const void* kv, c
                                      const int* cu_tokens, const int* start_pos, int n_requests, int n_tokens, int tiles,
                                      int H, int G, int d, int vd, int page_size, float scale, int window,
                                      const float* sinks, int splits, float* part_o, float* part_ml,
-                                     unsigned* tickets, cudaStream_t stream) {
+                                     unsigned* tickets, int chunk, const float* gate, long long gate_ld,
+                                     float out_scale, long long out_stride, cudaStream_t stream) {
   if (n_tokens <= 0 || n_requests <= 0) return 0;
   if (G <= 0 || H % G || H / G > TS_ROWS || d <= 0 || vd <= 0 || d > 128 || vd > 128 || d % 8 || vd % 8 ||
-      page_size <= 0 || splits < 1 || splits > 64 || G > 65535 || (splits > 1 && (!part_o || !part_ml)))
+      page_size <= 0 || splits < 1 || splits > 64 || G > 65535 || (splits > 1 && (!part_o || !part_ml)) ||
+      out_stride < (long long)H * vd || (out_stride & 1))
     return QD_ERR_UNSUPPORTED;
+  const AttnExtra ex = {chunk, gate, gate_ld, out_scale, out_stride};
   const float scale_log2 = scale * 1.4426950408889634f;
   int page_shift = -1;
   if ((page_size & (page_size - 1)) == 0)
@@ -597,7 +629,7 @@ extern "C" int qd_sink_attention_mma(const void* q, void* out, const void* kv, c
     }                                                                                                               \
     qd_launch(sink_attention_mma_kernel<D_, DV_>, grid, dim3(128), smem, stream, (const bf16*)q, (bf16*)out,          \
               (const bf16*)kv, block_table, max_blocks, cu_tokens, start_pos, n_requests, H, G, d, vd, page_size,    \
-              scale_log2, window, sinks, splits, part_o, part_ml, page_shift, tickets, single_tokens);               \
+              scale_log2, window, sinks, splits, part_o, part_ml, page_shift, tickets, single_tokens, ex);           \
   } while (0)
   if (d <= 64 && vd <= 64) TS_GO(64, 64);
   else if (d <= 64) TS_GO(64, 128);
@@ -608,7 +640,7 @@ extern "C" int qd_sink_attention_mma(const void* q, void* out, const void* kv, c
   if (splits > 1 && !tickets) {
     const int rows = n_tokens * H;
     qd_launch(sink_combine_kernel, dim3((rows + 3) / 4), dim3(128), 0, stream, (const float*)part_o,
-              (const float*)part_ml, sinks, (bf16*)out, rows, H, vd, splits);
+              (const float*)part_ml, sinks, (bf16*)out, rows, H, vd, splits, ex);
   }
   return qd_last_error();
 }

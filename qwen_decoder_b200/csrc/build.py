@@ -49,6 +49,8 @@ LIBRARIES: Dict[str, str] = {
     "attention_sink": "attention_sink.cu",
     "gated_block": "gated_block.cu",
     "attention_diff": "attention_diff.cu",
+    "qkv_prep": "qkv_prep.cu",
+    "time_mix": "time_mix.cu",
 }
 HEADERS = ["common.cuh", "entry_points.h"]
 # further files a library's source includes (hashed into its key)
@@ -56,6 +58,7 @@ EXTRA_DEPS: Dict[str, List[str]] = {
     "decode_attention_noalloc": ["attention_flash.cu", "decode_attention_noalloc.h"],
     "gated_block": ["short_conv.cuh"],
     "attention_diff": ["short_conv.cuh", "mma_sync.cuh"],
+    "qkv_prep": ["short_conv.cuh"],
     "attention_sink": ["mma_sync.cuh"],
 }
 

@@ -27,6 +27,7 @@ struct Addend {
   int dtype, n_parts;
   const float* unit_w;  // not null: the addend joins as p / sqrt(mean(p^2) + unit_eps) * unit_w[i]
   float unit_eps;
+  float mult;           // the addend (after its unit norm, if any) is multiplied by this constant
 };
 
 __device__ __forceinline__ float addend_at(const Addend& a, size_t stride, size_t i) {
@@ -40,7 +41,12 @@ struct TanhNorm {
   float alpha;
   void* out;            // [n_rows, D]; null: this norm is not computed
   int out_dtype;
+  int rms;              // 1: out = v / sqrt(mean(v^2) + eps) * w instead (b and alpha unused)
+  float eps;
 };
+__device__ __forceinline__ float row_norm(const TanhNorm& n, float v, int i, float fr) {
+  return n.rms ? v * fr * n.w[i] : fmaf(tanhf(n.alpha * v), n.w[i], n.b[i]);
+}
 
 // One CTA per output row r (source row s = rows[r] or r): v = x[s] + a0[s] + a1[s]; x[s] = v when write_back;
 // each norm with an ``out`` writes tanh(alpha v) w + b.
@@ -64,14 +70,28 @@ add_tanh_norm_kernel(float* __restrict__ x, Addend a0, Addend a1, TanhNorm n0, T
     for (int i = threadIdx.x; i < D; i += blockDim.x) { float v = addend_at(a1, stride, s * D + i); ss = fmaf(v, v, ss); }
     f1 = 1.0f / sqrtf(block_sum(ss, scratch) / (float)D + a1.unit_eps);
   }
-  for (int i = threadIdx.x; i < D; i += blockDim.x) {
+  f0 *= a0.mult;
+  f1 *= a1.mult;
+  const bool need_rms = (n0.out && n0.rms) || (n1.out && n1.rms);
+  float ssv = 0.f;
+  // the new sum: a thread computes the same elements in both passes, in the same way
+  auto sum_at = [&](int i) {
     float v = x[s * D + i];
-    if (a0.p) { float d = addend_at(a0, stride, s * D + i); v += a0.unit_w ? d * f0 * a0.unit_w[i] : d; }
-    if (a1.p) { float d = addend_at(a1, stride, s * D + i); v += a1.unit_w ? d * f1 * a1.unit_w[i] : d; }
+    if (a0.p) { float d = addend_at(a0, stride, s * D + i); v += a0.unit_w ? d * f0 * a0.unit_w[i] : d * f0; }
+    if (a1.p) { float d = addend_at(a1, stride, s * D + i); v += a1.unit_w ? d * f1 * a1.unit_w[i] : d * f1; }
+    return v;
+  };
+  if (need_rms) {
+    for (int i = threadIdx.x; i < D; i += blockDim.x) { const float v = sum_at(i); ssv = fmaf(v, v, ssv); }
+    ssv = block_sum(ssv, scratch);
+  }
+  const float fr0 = 1.0f / sqrtf(ssv / (float)D + n0.eps), fr1 = 1.0f / sqrtf(ssv / (float)D + n1.eps);
+  for (int i = threadIdx.x; i < D; i += blockDim.x) {
+    const float v = sum_at(i);
     if (write_back) x[s * D + i] = v;
     if (copy_out) st_code(copy_out, copy_dtype, (size_t)r * D + i, v);
-    if (n0.out) st_code(n0.out, n0.out_dtype, (size_t)r * D + i, fmaf(tanhf(n0.alpha * v), n0.w[i], n0.b[i]));
-    if (n1.out) st_code(n1.out, n1.out_dtype, (size_t)r * D + i, fmaf(tanhf(n1.alpha * v), n1.w[i], n1.b[i]));
+    if (n0.out) st_code(n0.out, n0.out_dtype, (size_t)r * D + i, row_norm(n0, v, i, fr0));
+    if (n1.out) st_code(n1.out, n1.out_dtype, (size_t)r * D + i, row_norm(n1, v, i, fr1));
   }
 }
 
@@ -99,8 +119,10 @@ __device__ __forceinline__ float4 addend4_at(const Addend& a, size_t stride, siz
   }
   return v;
 }
-__device__ __forceinline__ float4 tanh_norm4(const TanhNorm& n, float4 v, int i) {
-  const float4 w = *reinterpret_cast<const float4*>(n.w + i), b = *reinterpret_cast<const float4*>(n.b + i);
+__device__ __forceinline__ float4 tanh_norm4(const TanhNorm& n, float4 v, int i, float fr) {
+  const float4 w = *reinterpret_cast<const float4*>(n.w + i);
+  if (n.rms) return make_float4(v.x * fr * w.x, v.y * fr * w.y, v.z * fr * w.z, v.w * fr * w.w);
+  const float4 b = *reinterpret_cast<const float4*>(n.b + i);
   return make_float4(fmaf(tanhf(n.alpha * v.x), w.x, b.x), fmaf(tanhf(n.alpha * v.y), w.y, b.y),
                      fmaf(tanhf(n.alpha * v.z), w.z, b.z), fmaf(tanhf(n.alpha * v.w), w.w, b.w));
 }
@@ -132,6 +154,9 @@ add_tanh_norm_vec_kernel(float* __restrict__ x, Addend a0, Addend a1, TanhNorm n
   float f0 = 1.f, f1 = 1.f;
   if (a0.p && a0.unit_w) f0 = 1.0f / sqrtf(block_sum(ss0, scratch) / (float)D + a0.unit_eps);
   if (a1.p && a1.unit_w) f1 = 1.0f / sqrtf(block_sum(ss1, scratch) / (float)D + a1.unit_eps);
+  f0 *= a0.mult;
+  f1 *= a1.mult;
+  float ssv = 0.f;
 #pragma unroll
   for (int k = 0; k < VPT; k++) {
     const int i = (threadIdx.x + k * 256) * 4;
@@ -142,7 +167,8 @@ add_tanh_norm_vec_kernel(float* __restrict__ x, Addend a0, Addend a1, TanhNorm n
       if (a0.unit_w) {
         const float4 u = *reinterpret_cast<const float4*>(a0.unit_w + i);
         d = make_float4(d.x * f0 * u.x, d.y * f0 * u.y, d.z * f0 * u.z, d.w * f0 * u.w);
-      }
+      } else
+        d = make_float4(d.x * f0, d.y * f0, d.z * f0, d.w * f0);
       v.x += d.x; v.y += d.y; v.z += d.z; v.w += d.w;
     }
     if (a1.p) {
@@ -150,30 +176,41 @@ add_tanh_norm_vec_kernel(float* __restrict__ x, Addend a0, Addend a1, TanhNorm n
       if (a1.unit_w) {
         const float4 u = *reinterpret_cast<const float4*>(a1.unit_w + i);
         d = make_float4(d.x * f1 * u.x, d.y * f1 * u.y, d.z * f1 * u.z, d.w * f1 * u.w);
-      }
+      } else
+        d = make_float4(d.x * f1, d.y * f1, d.z * f1, d.w * f1);
       v.x += d.x; v.y += d.y; v.z += d.z; v.w += d.w;
     }
+    xv[k] = v;
+    ssv += v.x * v.x + v.y * v.y + v.z * v.z + v.w * v.w;
     if (write_back) *reinterpret_cast<float4*>(x + s * D + i) = v;
     if (copy_out) st4_code(copy_out, copy_dtype, (size_t)r * D + i, v);
-    if (n0.out) st4_code(n0.out, n0.out_dtype, (size_t)r * D + i, tanh_norm4(n0, v, i));
-    if (n1.out) st4_code(n1.out, n1.out_dtype, (size_t)r * D + i, tanh_norm4(n1, v, i));
+  }
+  if ((n0.out && n0.rms) || (n1.out && n1.rms)) ssv = block_sum(ssv, scratch);
+  const float fr0 = 1.0f / sqrtf(ssv / (float)D + n0.eps), fr1 = 1.0f / sqrtf(ssv / (float)D + n1.eps);
+#pragma unroll
+  for (int k = 0; k < VPT; k++) {
+    const int i = (threadIdx.x + k * 256) * 4;
+    if (i >= D) continue;
+    if (n0.out) st4_code(n0.out, n0.out_dtype, (size_t)r * D + i, tanh_norm4(n0, xv[k], i, fr0));
+    if (n1.out) st4_code(n1.out, n1.out_dtype, (size_t)r * D + i, tanh_norm4(n1, xv[k], i, fr1));
   }
 }
 
 // x [T, D] float32 (updated when write_back).  Addend k: ak [nk, T, D] of dtype code ak_dtype, null for none; with
 // ak_unit_w it joins unit-normalised.  Norm k: wk, bk [D] float32, alphak, outk [n_rows, D] (null: not computed).
+// An addend is multiplied by its ``mult``; a norm with ``rms`` set is out = v / sqrt(mean(v^2) + eps) * w instead.
 // rows: int32 [n_rows] source rows, or null for all T rows in order.  copy_out [n_rows, D]: the new sum itself in
 // dtype copy_dtype (null: not written).
 extern "C" int qd_add_tanh_norm(float* x, int T, int D,
-                                const void* a0, int a0_dtype, int a0_parts, const float* a0_unit_w, float a0_eps,
-                                const void* a1, int a1_dtype, int a1_parts, const float* a1_unit_w, float a1_eps,
-                                const float* w0, const float* b0, float alpha0, void* out0, int out0_dtype,
-                                const float* w1, const float* b1, float alpha1, void* out1, int out1_dtype,
+                                const void* a0, int a0_dtype, int a0_parts, const float* a0_unit_w, float a0_eps, float a0_mult,
+                                const void* a1, int a1_dtype, int a1_parts, const float* a1_unit_w, float a1_eps, float a1_mult,
+                                const float* w0, const float* b0, float alpha0, void* out0, int out0_dtype, int rms0, float eps0,
+                                const float* w1, const float* b1, float alpha1, void* out1, int out1_dtype, int rms1, float eps1,
                                 const int* rows, int n_rows, int write_back, void* copy_out, int copy_dtype,
                                 cudaStream_t stream) {
   if (n_rows <= 0) return 0;
-  Addend A0 = {a0, a0_dtype, a0_parts, a0_unit_w, a0_eps}, A1 = {a1, a1_dtype, a1_parts, a1_unit_w, a1_eps};
-  TanhNorm N0 = {w0, b0, alpha0, out0, out0_dtype}, N1 = {w1, b1, alpha1, out1, out1_dtype};
+  Addend A0 = {a0, a0_dtype, a0_parts, a0_unit_w, a0_eps, a0_mult}, A1 = {a1, a1_dtype, a1_parts, a1_unit_w, a1_eps, a1_mult};
+  TanhNorm N0 = {w0, b0, alpha0, out0, out0_dtype, rms0, eps0}, N1 = {w1, b1, alpha1, out1, out1_dtype, rms1, eps1};
   const uintptr_t all = (uintptr_t)x | (uintptr_t)a0 | (uintptr_t)a1 | (uintptr_t)a0_unit_w | (uintptr_t)a1_unit_w |
                         (uintptr_t)w0 | (uintptr_t)b0 | (uintptr_t)out0 | (uintptr_t)w1 | (uintptr_t)b1 |
                         (uintptr_t)out1 | (uintptr_t)copy_out;

@@ -1,0 +1,219 @@
+// A recurrent mixer with a matrix state per head and a per-channel, per-token decay, for a flat batch of portions:
+//
+//   shift_mix  x_s[t] = h[t] + (h[t-1] - h[t]) * mu_s for each of n_mix blends s; h[t-1] of a portion's first token is
+//              the request's kept input (its state row), zeros at a sequence's start
+//   decay      w[t, c] = exp(-exp(w0[c] + sum_r tanh(a[t, r]) W2[c, r])), a the float32 sums of the low-rank product
+//   scan       per (request, head), token by token:  o_t = (S + diag(u) k_t v_t^T)^T r_t;  S <- diag(w_t) S + k_t v_t^T
+//              S [d, dv] float32 lives in the request's state row, is read once and written once per step
+//   finish     out[t, head] = o / sqrt(mean(o^2) + eps) * norm * silu(g) * out_scale, rounded once for the output
+//              projection; the last token of every portion leaves its h as the request's kept input
+//
+// Everything between the projections' float32 sums and ``finish``'s store is float32; the recurrence runs in the
+// order of the tokens with a fixed order of additions, so a portion at once and token by token agree bit for bit.
+#include "common.cuh"
+#include <math.h>
+
+__device__ __forceinline__ float tm_ld(const void* p, int code, size_t i) {
+  return code == QD_F32 ? reinterpret_cast<const float*>(p)[i] : __bfloat162float(reinterpret_cast<const bf16*>(p)[i]);
+}
+__device__ __forceinline__ void tm_st(void* p, int code, size_t i, float v) {
+  if (code == QD_F32) reinterpret_cast<float*>(p)[i] = v;
+  else reinterpret_cast<bf16*>(p)[i] = __float2bfloat16_rn(v);
+}
+
+// ------------------------------------------------------------------------------------------------------ shift_mix
+// grid (ceil(D / 256), T).  h [T, D] (``dtype``); mu float32 [n_mix, D]; out [n_mix, T, D] (``dtype``).
+__global__ void __launch_bounds__(256)
+tm_shift_mix_kernel(const void* __restrict__ h, int dtype, int T, int D, const float* __restrict__ mu, int n_mix,
+                    const float* __restrict__ state, long long state_stride, long long prev_off,
+                    const int* __restrict__ token_req, const int* __restrict__ cu_tokens,
+                    const int* __restrict__ slots, void* __restrict__ out) {
+  pdl_launch_dependents();
+  pdl_wait();
+  const int c = blockIdx.x * blockDim.x + threadIdx.x, t = blockIdx.y;
+  if (c >= D) return;
+  const int r = token_req[t];
+  const float cur = tm_ld(h, dtype, (size_t)t * D + c);
+  const float prev = t > cu_tokens[r] ? tm_ld(h, dtype, (size_t)(t - 1) * D + c)
+                                      : state[(size_t)slots[r] * state_stride + prev_off + c];
+  const float diff = prev - cur;
+  for (int s = 0; s < n_mix; s++)
+    tm_st(out, dtype, ((size_t)s * T + t) * D + c, fmaf(diff, mu[(size_t)s * D + c], cur));
+}
+
+extern "C" int qd_tm_shift_mix(const void* h, int dtype, int T, int D, const float* mu, int n_mix, const float* state,
+                               long long state_stride, long long prev_off, const int* token_req, const int* cu_tokens,
+                               const int* slots, void* out, cudaStream_t stream) {
+  if (T <= 0) return 0;
+  if (T > 65535 || D <= 0 || n_mix <= 0 || !state) return QD_ERR_UNSUPPORTED;
+  qd_launch(tm_shift_mix_kernel, dim3((D + 255) / 256, T), dim3(256), 0, stream, h, dtype, T, D, mu, n_mix, state,
+            state_stride, prev_off, token_req, cu_tokens, slots, out);
+  return qd_last_error();
+}
+
+// ---------------------------------------------------------------------------------------------------------- decay
+// grid (ceil(C / 128), T).  a float32 [T, lda] (the first R columns); w2 [C, R] (``w_dtype``); w0 float32 [C].
+__global__ void __launch_bounds__(128)
+tm_decay_kernel(const float* __restrict__ a, long long lda, int R, const void* __restrict__ w2, int w_dtype,
+                const float* __restrict__ w0, int C, float* __restrict__ out) {
+  pdl_launch_dependents();
+  pdl_wait();
+  extern __shared__ float th[];
+  const int t = blockIdx.y;
+  for (int i = threadIdx.x; i < R; i += blockDim.x) th[i] = tanhf(a[(size_t)t * lda + i]);
+  __syncthreads();
+  const int c = blockIdx.x * blockDim.x + threadIdx.x;
+  if (c >= C) return;
+  float z = w0[c];
+  for (int i = 0; i < R; i++) z = fmaf(th[i], tm_ld(w2, w_dtype, (size_t)c * R + i), z);
+  out[(size_t)t * C + c] = expf(-expf(z));
+}
+
+extern "C" int qd_tm_decay(const float* a, long long lda, int T, int R, const void* w2, int w_dtype, const float* w0,
+                           int C, float* out, cudaStream_t stream) {
+  if (T <= 0) return 0;
+  if (T > 65535 || R <= 0 || R > 8192 || C <= 0) return QD_ERR_UNSUPPORTED;
+  qd_launch(tm_decay_kernel, dim3((C + 127) / 128, T), dim3(128), (size_t)R * sizeof(float), stream, a, lda, R, w2,
+            w_dtype, w0, C, out);
+  return qd_last_error();
+}
+
+// ----------------------------------------------------------------------------------------------------------- scan
+// grid (ceil(dv / 16), H, requests), 256 threads: thread (x = tid & 15, column = tid >> 4) keeps NI elements
+// S[x + 16 n, column] of the state in registers.  r, k, w of TM_ROUND tokens arrive in shared memory per round; a
+// token then costs NI x 4 FMAs a thread and a reduction over the 16 threads of a column.
+#define TM_ROUND 8
+
+template <int NI>
+__global__ void __launch_bounds__(256)
+tm_scan_kernel(const float* __restrict__ r_, const float* __restrict__ k_, const float* __restrict__ v_, long long ld,
+               const float* __restrict__ w_, const float* __restrict__ u_, int H, int d, int dv,
+               float* __restrict__ state, long long state_stride, long long s_off, const int* __restrict__ cu_tokens,
+               const int* __restrict__ slots, float* __restrict__ out, int write_state) {
+  pdl_launch_dependents();
+  pdl_wait();
+  extern __shared__ float tm_sm[];                    // [TM_ROUND][3][d] r, k, w; then [TM_ROUND][16] v
+  float* vs = tm_sm + (size_t)TM_ROUND * 3 * d;
+  const int tid = threadIdx.x, x = tid & 15, jl = tid >> 4;
+  const int h = blockIdx.y, req = blockIdx.z, j = blockIdx.x * 16 + jl;
+  const bool live = j < dv;
+  const int t0 = cu_tokens[req], t1 = cu_tokens[req + 1];
+  if (t0 >= t1) return;
+  float* S = state + (size_t)slots[req] * state_stride + s_off + (size_t)h * d * dv;
+  float s[NI], uu[NI];
+#pragma unroll
+  for (int n = 0; n < NI; n++) {
+    const int i = x + 16 * n;
+    s[n] = (live && i < d) ? S[(size_t)i * dv + j] : 0.f;
+    uu[n] = i < d ? u_[(size_t)h * d + i] : 0.f;
+  }
+  for (int tb = t0; tb < t1; tb += TM_ROUND) {
+    const int nt = min(TM_ROUND, t1 - tb);
+    __syncthreads();
+    for (int e = tid; e < nt * d; e += 256) {
+      const int tt = e / d, i = e - tt * d;
+      const size_t src = (size_t)(tb + tt) * ld + (size_t)h * d + i;
+      tm_sm[(tt * 3 + 0) * d + i] = r_[src];
+      tm_sm[(tt * 3 + 1) * d + i] = k_[src];
+      tm_sm[(tt * 3 + 2) * d + i] = w_[(size_t)(tb + tt) * H * d + (size_t)h * d + i];
+    }
+    if (tid < nt * 16) {
+      const int tt = tid >> 4, jj = blockIdx.x * 16 + (tid & 15);
+      vs[tid] = jj < dv ? v_[(size_t)(tb + tt) * ld + (size_t)h * dv + jj] : 0.f;
+    }
+    __syncthreads();
+    for (int tt = 0; tt < nt; tt++) {
+      const float vj = vs[tt * 16 + jl];
+      const float *rs = tm_sm + (tt * 3) * d, *ks = rs + d, *ws = ks + d;
+      float acc = 0.f;
+#pragma unroll
+      for (int n = 0; n < NI; n++) {
+        const int i = x + 16 * n;
+        if (i < d) {
+          const float kv = ks[i] * vj;
+          acc = fmaf(rs[i], fmaf(uu[n], kv, s[n]), acc);
+          s[n] = fmaf(ws[i], s[n], kv);
+        }
+      }
+      acc += __shfl_xor_sync(0xffffffffu, acc, 8);
+      acc += __shfl_xor_sync(0xffffffffu, acc, 4);
+      acc += __shfl_xor_sync(0xffffffffu, acc, 2);
+      acc += __shfl_xor_sync(0xffffffffu, acc, 1);
+      if (x == 0 && live) out[(size_t)(tb + tt) * H * dv + (size_t)h * dv + j] = acc;
+    }
+  }
+  if (write_state && live) {
+#pragma unroll
+    for (int n = 0; n < NI; n++) {
+      const int i = x + 16 * n;
+      if (i < d) S[(size_t)i * dv + j] = s[n];
+    }
+  }
+}
+
+// r, k [T, >= H*d] and v [T, >= H*dv] float32 with rows ``ld`` apart (each pointer at its own first column);
+// w float32 [T, H*d] dense; u float32 [H, d]; out float32 [T, H*dv] dense; state float32 rows ``state_stride`` apart,
+// the heads' matrices [H, d, dv] at ``s_off``.
+extern "C" int qd_tm_scan(const float* r, const float* k, const float* v, long long ld, const float* w, const float* u,
+                          int H, int d, int dv, float* state, long long state_stride, long long s_off,
+                          const int* cu_tokens, const int* slots, int n_requests, float* out, int write_state,
+                          cudaStream_t stream) {
+  if (n_requests <= 0) return 0;
+  if (H <= 0 || H > 65535 || n_requests > 65535 || d <= 0 || d > 256 || dv <= 0) return QD_ERR_UNSUPPORTED;
+  dim3 grid((dv + 15) / 16, H, n_requests);
+  const size_t smem = ((size_t)TM_ROUND * 3 * d + TM_ROUND * 16) * sizeof(float);
+#define TM_GO(NI)                                                                                                  \
+  qd_launch(tm_scan_kernel<NI>, grid, dim3(256), smem, stream, r, k, v, ld, w, u, H, d, dv, state, state_stride,   \
+            s_off, cu_tokens, slots, out, write_state)
+  if (d <= 16) TM_GO(1);
+  else if (d <= 32) TM_GO(2);
+  else if (d <= 64) TM_GO(4);
+  else if (d <= 128) TM_GO(8);
+  else TM_GO(16);
+#undef TM_GO
+  return qd_last_error();
+}
+
+// --------------------------------------------------------------------------------------------------------- finish
+// grid (T), 256 threads: a warp per head in turn.  o float32 [T, H*dv]; g float32 [T, ldg] gate logits (silu is taken
+// here); norm float32 [H*dv]; out rows ``out_stride`` apart in ``out_dtype``.  The last token of a portion copies
+// its row of h [T, D] (``h_dtype``) into the request's state row at ``prev_off``.
+__global__ void __launch_bounds__(256)
+tm_finish_kernel(const float* __restrict__ o, const float* __restrict__ g, long long ldg,
+                 const float* __restrict__ norm, int H, int dv, float eps, float out_scale, void* __restrict__ out,
+                 int out_dtype, long long out_stride, const void* __restrict__ h, int h_dtype, int D,
+                 float* __restrict__ state, long long state_stride, long long prev_off,
+                 const int* __restrict__ token_req, const int* __restrict__ cu_tokens, const int* __restrict__ slots,
+                 int write_state) {
+  pdl_launch_dependents();
+  pdl_wait();
+  const int t = blockIdx.x, warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  for (int hd = warp; hd < H; hd += 8) {
+    const size_t base = (size_t)t * H * dv + (size_t)hd * dv;
+    float ss = 0.f;
+    for (int i = lane; i < dv; i += 32) { const float y = o[base + i]; ss = fmaf(y, y, ss); }
+    const float f = out_scale / sqrtf(warp_sum(ss) / (float)dv + eps);
+    for (int i = lane; i < dv; i += 32) {
+      const float z = g[(size_t)t * ldg + (size_t)hd * dv + i];
+      const float gate = z / (1.0f + expf(-z));
+      tm_st(out, out_dtype, (size_t)t * out_stride + (size_t)hd * dv + i, o[base + i] * f * norm[hd * dv + i] * gate);
+    }
+  }
+  if (!write_state) return;
+  const int r = token_req[t];
+  if (t != cu_tokens[r + 1] - 1) return;
+  float* prev = state + (size_t)slots[r] * state_stride + prev_off;
+  for (int c = threadIdx.x; c < D; c += blockDim.x) prev[c] = tm_ld(h, h_dtype, (size_t)t * D + c);
+}
+
+extern "C" int qd_tm_finish(const float* o, const float* g, long long ldg, const float* norm, int T, int H, int dv,
+                            float eps, float out_scale, void* out, int out_dtype, long long out_stride, const void* h,
+                            int h_dtype, int D, float* state, long long state_stride, long long prev_off,
+                            const int* token_req, const int* cu_tokens, const int* slots, int write_state,
+                            cudaStream_t stream) {
+  if (T <= 0) return 0;
+  if (H <= 0 || dv <= 0 || !state) return QD_ERR_UNSUPPORTED;
+  qd_launch(tm_finish_kernel, dim3(T), dim3(256), 0, stream, o, g, ldg, norm, H, dv, eps, out_scale, out, out_dtype,
+            out_stride, h, h_dtype, D, state, state_stride, prev_off, token_req, cu_tokens, slots, write_state);
+  return qd_last_error();
+}

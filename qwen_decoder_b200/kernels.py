@@ -1154,8 +1154,10 @@ def add_tanh_norm(x: torch.Tensor, addends, norms, rows: Optional[torch.Tensor] 
     """One launch over the rows of the residual sum x (float32 [T, D]): v = x + the pending ``addends``; x = v when
     ``write_back``; every norm (w, b, alpha, out) of ``norms`` writes out = tanh(alpha v) w + b; ``copy_out`` gets v
     itself in its own dtype.  ``addends``: up to two of (tensor [T, D] or float32 partial sums [n, T, D], unit) where
-    unit is None or (u float32 [D], eps): the addend then joins as a / sqrt(mean(a^2) + eps) * u.  ``rows`` (int32):
-    only these rows, outputs in their order."""
+    unit is None or (u float32 [D], eps): the addend then joins as a / sqrt(mean(a^2) + eps) * u; a third element
+    ``mult`` multiplies the addend by a constant.  A norm given as ("rms", w, eps, out) writes
+    out = v / sqrt(mean(v^2) + eps) * w instead of the tanh form.  ``rows`` (int32): only these rows, outputs in their
+    order."""
     T, D = x.shape
     assert x.dtype == torch.float32 and len(addends) <= 2 and len(norms) <= 2
     _contig(x, "x")
@@ -1163,23 +1165,29 @@ def add_tanh_norm(x: torch.Tensor, addends, norms, rows: Optional[torch.Tensor] 
     args = [_ptr(x), _I(T), _I(D)]
     for k in range(2):
         if k < len(addends):
-            a, unit = addends[k]
+            a, unit = addends[k][:2]
+            mult = float(addends[k][2]) if len(addends[k]) > 2 else 1.0
             parts = a.shape[0] if a.dim() == 3 else 1
             assert tuple(a.shape[-2:]) == (T, D) and (parts == 1 or a.dtype == torch.float32)
             _contig(a, "addend")
             uw, ue = unit if unit is not None else (None, 0.0)
             assert uw is None or (uw.dtype == torch.float32 and uw.numel() == D)
-            args += [_ptr(a), _I(dtype_code(a.dtype)), _I(parts), _ptr(uw), _F(ue)]
+            args += [_ptr(a), _I(dtype_code(a.dtype)), _I(parts), _ptr(uw), _F(ue), _F(mult)]
         else:
-            args += [_ptr(None), _I(0), _I(1), _ptr(None), _F(0.0)]
+            args += [_ptr(None), _I(0), _I(1), _ptr(None), _F(0.0), _F(1.0)]
     for k in range(2):
-        if k < len(norms):
+        if k < len(norms) and isinstance(norms[k][0], str):
+            _, w, eps, out = norms[k]
+            assert w.dtype == torch.float32 and w.numel() == D and out.shape == (n_rows, D)
+            _contig(out, "out")
+            args += [_ptr(w), _ptr(None), _F(0.0), _ptr(out), _I(dtype_code(out.dtype)), _I(1), _F(eps)]
+        elif k < len(norms):
             w, b, alpha, out = norms[k]
             assert w.dtype == b.dtype == torch.float32 and w.numel() == b.numel() == D and out.shape == (n_rows, D)
             _contig(out, "out")
-            args += [_ptr(w), _ptr(b), _F(alpha), _ptr(out), _I(dtype_code(out.dtype))]
+            args += [_ptr(w), _ptr(b), _F(alpha), _ptr(out), _I(dtype_code(out.dtype)), _I(0), _F(0.0)]
         else:
-            args += [_ptr(None), _ptr(None), _F(0.0), _ptr(None), _I(0)]
+            args += [_ptr(None), _ptr(None), _F(0.0), _ptr(None), _I(0), _I(0), _F(0.0)]
     if copy_out is not None:
         assert copy_out.shape == (n_rows, D)
         _contig(copy_out, "copy_out")
@@ -1243,20 +1251,26 @@ def qk_norm_rope_write(qkv: torch.Tensor, H: int, G: int, d: int, vd: int, wq: O
 
 def sink_attention_generic(q: torch.Tensor, out: torch.Tensor, kv: torch.Tensor, block_table: torch.Tensor,
                            token_req: torch.Tensor, positions: torch.Tensor, H: int, G: int, d: int, vd: int,
-                           page_size: int, scale: float, window: int, sinks: Optional[torch.Tensor]) -> None:
-    """Attention of every token over keys 0..pos (or the last ``window``) of its request with a sink in the softmax's
-    denominator (``sinks`` float32 [H], or None), values of size ``vd``; q [T, H*d], out [T, H*vd]; float32
-    arithmetic, any sizes."""
+                           page_size: int, scale: float, window: int, sinks: Optional[torch.Tensor], chunk: int = 0,
+                           gate: Optional[torch.Tensor] = None, out_scale: float = 1.0) -> None:
+    """Attention of every token over keys 0..pos (or the last ``window``; with ``chunk`` only those of the query's
+    own block of ``chunk`` positions) of its request with a sink in the softmax's denominator (``sinks`` float32 [H],
+    or None), values of size ``vd``; q [T, H*d], out [T, H*vd] (rows may be strided: a column range of a wider
+    tensor); head h's output is multiplied by ``out_scale`` and, with ``gate`` (float32 [T, >= H] logits, rows may be
+    strided), by sigmoid(gate[t, h]); float32 arithmetic, any sizes."""
     T = q.shape[0]
     assert q.shape == (T, H * d) and out.shape == (T, H * vd) and q.dtype == out.dtype == kv.dtype
+    assert q.stride(1) == 1 and out.stride(1) == 1
+    assert gate is None or (gate.dtype == torch.float32 and gate.shape[0] == T and gate.stride(1) == 1)
     assert kv.numel() % (G * page_size * (d + vd)) == 0
     assert block_table.dtype == torch.int32 and block_table.dim() == 2
     assert sinks is None or (sinks.dtype == torch.float32 and sinks.numel() == H)
-    _contig(q, "q"); _contig(out, "out"); _contig(kv, "kv"); _contig(block_table, "block_table")
+    _contig(kv, "kv"); _contig(block_table, "block_table")
     _check(library("attention_sink").qd_sink_attention_generic(
         _ptr(q), _LL(q.stride(0)), _ptr(out), _LL(out.stride(0)), _ptr(kv), _I(dtype_code(q.dtype)), _ptr(block_table),
         _I(block_table.shape[1]), _ptr(token_req), _ptr(positions), _I(T), _I(H), _I(G), _I(d), _I(vd), _I(page_size),
-        _F(scale), _I(window), _ptr(sinks), _stream()), "sink_attention_generic")
+        _F(scale), _I(window), _ptr(sinks), _I(chunk), _ptr(gate), _LL(gate.stride(0) if gate is not None else 0),
+        _F(out_scale), _stream()), "sink_attention_generic")
 
 
 SINK_MMA_ROWS = 64       # rows, (token, head within the group) pairs, of one tile of the tensor-core kernel
@@ -1272,16 +1286,20 @@ def sink_mma_supported(dtype: torch.dtype, H: int, G: int, d: int, vd: int) -> b
 def sink_attention_mma(q: torch.Tensor, out: torch.Tensor, kv: torch.Tensor, block_table: torch.Tensor,
                        cu_tokens: torch.Tensor, start_pos: torch.Tensor, n_requests: int, n_tokens: int, H: int, G: int,
                        d: int, vd: int, page_size: int, scale: float, window: int, sinks: Optional[torch.Tensor],
-                       splits: int = 1) -> None:
+                       splits: int = 1, chunk: int = 0, gate: Optional[torch.Tensor] = None,
+                       out_scale: float = 1.0) -> None:
     """``sink_attention_generic`` on tensor cores for portions of ``n_requests`` requests (rows cu_tokens[r] ..
     cu_tokens[r+1]-1 of q and out, at positions start_pos[r]..): a decoded token is a portion of one.  ``splits`` > 1
-    shares every tile's keys among that many CTAs (for steps of few tokens over long contexts)."""
+    shares every tile's keys among that many CTAs (for steps of few tokens over long contexts).  ``chunk``, ``gate``,
+    ``out_scale`` and strided rows of ``out`` as for the generic kernel."""
     assert q.dtype == out.dtype == kv.dtype == torch.bfloat16 and q.shape[1] == H * d and out.shape[1] == H * vd
+    assert out.stride(1) == 1 and out.stride(0) % 2 == 0
+    assert gate is None or (gate.dtype == torch.float32 and gate.stride(1) == 1)
     assert kv.numel() % (G * page_size * (d + vd)) == 0
     assert block_table.dtype == torch.int32 and block_table.dim() == 2 and block_table.shape[0] >= n_requests
     assert cu_tokens.dtype == torch.int32 and start_pos.dtype == torch.int32
     assert sinks is None or (sinks.dtype == torch.float32 and sinks.numel() == H)
-    _contig(q, "q"); _contig(out, "out"); _contig(kv, "kv"); _contig(block_table, "block_table")
+    _contig(q, "q"); _contig(kv, "kv"); _contig(block_table, "block_table")
     ntok = SINK_MMA_ROWS // (H // G)
     tiles = n_tokens // ntok + n_requests            # at least sum over requests of ceil(tokens / ntok)
     part_o = part_ml = tickets = None
@@ -1296,9 +1314,114 @@ def sink_attention_mma(q: torch.Tensor, out: torch.Tensor, kv: torch.Tensor, blo
     _check(library("attention_sink").qd_sink_attention_mma(
         _ptr(q), _ptr(out), _ptr(kv), _ptr(block_table), _I(block_table.shape[1]), _ptr(cu_tokens), _ptr(start_pos),
         _I(n_requests), _I(n_tokens), _I(tiles), _I(H), _I(G), _I(d), _I(vd), _I(page_size), _F(scale), _I(window),
-        _ptr(sinks), _I(splits), _ptr(part_o), _ptr(part_ml), _ptr(tickets), _stream()), "sink_attention_mma")
+        _ptr(sinks), _I(splits), _ptr(part_o), _ptr(part_ml), _ptr(tickets), _I(chunk), _ptr(gate),
+        _LL(gate.stride(0) if gate is not None else 0), _F(out_scale), _LL(out.stride(0)), _stream()),
+        "sink_attention_mma")
     if splits > 1 and tickets is None:
         _launch_count[0] += 1
+
+
+# ------------------------------------------------------------------ between the q/k/v product and attention
+QKV_NORMS = {"none": 0, "whole": 1, "head": 2}
+
+
+def qkv_prep(u: torch.Tensor, H: int, G: int, d: int, vd: int, conv_w: Optional[torch.Tensor],
+             state: Optional[torch.Tensor], state_off: int, ctx, update_state: bool, norm: str, norm_after: bool,
+             wq: Optional[torch.Tensor], wk: Optional[torch.Tensor], eps: float, rotary_dim: int, pairing: int,
+             cos: Optional[torch.Tensor], sin: Optional[torch.Tensor], q_out: torch.Tensor, kv: torch.Tensor,
+             slot_map: torch.Tensor, page_size: int, write_kv: bool) -> None:
+    """From the float32 sums u [T, >= C], C = H*d + G*d + G*vd (q | k | v): every channel through a short causal
+    convolution (``conv_w`` float32 [C, taps] or None; the last taps - 1 inputs of every request live at ``state_off``
+    of its row of ``state`` and are moved on when ``update_state``); ``norm`` "whole": q and k divided by their root
+    mean square over the whole projection times wq [H*d] / wk [G*d], before the rotation; "head": every head divided
+    by its own, without weights, after the rotation when ``norm_after``; the first ``rotary_dim`` elements of every
+    head of q and k turned by the table rows of ``ctx.positions``; q to q_out [T, H*d], k and v to the token's slot of
+    ``kv`` (pages of [G, page_size, d] keys then [G, page_size, vd] values)."""
+    T = u.shape[0]
+    C = H * d + G * d + G * vd
+    assert u.dtype == torch.float32 and u.shape[1] >= C and u.stride(1) == 1
+    assert q_out.shape == (T, H * d) and q_out.is_contiguous()
+    taps = 0
+    if conv_w is not None:
+        taps = conv_w.shape[1]
+        assert conv_w.shape == (C, taps) and conv_w.dtype == torch.float32 and conv_w.is_contiguous()
+        assert taps == 1 or (state is not None and state.dtype == torch.float32 and state.is_contiguous())
+    if norm == "whole":
+        assert wq.dtype == wk.dtype == torch.float32 and wq.numel() == H * d and wk.numel() == G * d
+    if rotary_dim:
+        assert cos.dtype == sin.dtype == torch.float32 and cos.shape[1] == rotary_dim // 2
+    if write_kv:
+        assert kv.numel() % (G * page_size * (d + vd)) == 0 and slot_map.dtype == torch.int32
+        _contig(kv, "kv")
+    _check(library("qkv_prep").qd_qkv_prep(
+        _ptr(u), _LL(u.stride(0)), _I(T), _I(ctx.num_requests), _I(H), _I(G), _I(d), _I(vd), _I(taps), _ptr(conv_w),
+        _ptr(state if taps > 1 else None), _LL(state.stride(0) if state is not None else 0), _LL(state_off),
+        _ptr(ctx.token_request), _ptr(ctx.cu_tokens), _ptr(ctx.state_slots), _I(1 if update_state else 0),
+        _I(QKV_NORMS[norm]), _I(1 if norm_after else 0), _ptr(wq), _ptr(wk), _F(eps), _I(rotary_dim), _I(pairing),
+        _ptr(cos), _ptr(sin), _ptr(ctx.positions), _ptr(q_out), _I(dtype_code(q_out.dtype)), _ptr(kv),
+        _I(dtype_code(kv.dtype)), _ptr(slot_map), _I(page_size), _I(1 if write_kv else 0), _stream()), "qkv_prep")
+    if update_state and taps > 1 and T != ctx.num_requests:
+        _launch_count[0] += 1
+
+
+# ------------------------------------------------------------------ the recurrent mixer with a matrix state
+def tm_shift_mix(h: torch.Tensor, mu: torch.Tensor, state: torch.Tensor, prev_off: int, ctx, out: torch.Tensor) -> None:
+    """out[s, t] = h[t] + (h[t-1] - h[t]) * mu[s]; the row before a portion's first token is the request's kept input
+    (``state`` float32 [slots, n], D numbers at ``prev_off``).  h [T, D], mu float32 [n_mix, D], out [n_mix, T, D]."""
+    T, D = h.shape
+    n = mu.shape[0]
+    assert mu.shape == (n, D) and mu.dtype == torch.float32 and out.shape == (n, T, D) and out.dtype == h.dtype
+    assert state.dtype == torch.float32
+    _contig(h, "h"); _contig(mu, "mu"); _contig(out, "out"); _contig(state, "state")
+    _check(library("time_mix").qd_tm_shift_mix(
+        _ptr(h), _I(dtype_code(h.dtype)), _I(T), _I(D), _ptr(mu), _I(n), _ptr(state), _LL(state.stride(0)),
+        _LL(prev_off), _ptr(ctx.token_request), _ptr(ctx.cu_tokens), _ptr(ctx.state_slots), _ptr(out), _stream()),
+        "tm_shift_mix")
+
+
+def tm_decay(a: torch.Tensor, w2: torch.Tensor, w0: torch.Tensor, out: torch.Tensor) -> None:
+    """out[t, c] = exp(-exp(w0[c] + sum_r tanh(a[t, r]) w2[c, r])); a float32 [T, R] (rows may be strided), w2 [C, R],
+    w0 float32 [C], out float32 [T, C]."""
+    T, R = a.shape
+    C = w2.shape[0]
+    assert a.dtype == torch.float32 and a.stride(1) == 1 and w2.shape == (C, R) and w0.dtype == torch.float32
+    assert w0.numel() == C and out.shape == (T, C) and out.dtype == torch.float32
+    _contig(w2, "w2"); _contig(out, "out")
+    _check(library("time_mix").qd_tm_decay(_ptr(a), _LL(a.stride(0)), _I(T), _I(R), _ptr(w2), _I(dtype_code(w2.dtype)),
+                                           _ptr(w0), _I(C), _ptr(out), _stream()), "tm_decay")
+
+
+def tm_scan(r: torch.Tensor, k: torch.Tensor, v: torch.Tensor, w: torch.Tensor, u: torch.Tensor, H: int, d: int,
+            state: torch.Tensor, s_off: int, ctx, out: torch.Tensor, write_state: bool) -> None:
+    """Per (request, head), token by token: o_t = (S + diag(u) k_t v_t^T)^T r_t; S <- diag(w_t) S + k_t v_t^T.
+    r, k, v float32 [T, H*d] with one common row stride (column ranges of one tensor), w float32 [T, H*d] dense,
+    u float32 [H, d], out float32 [T, H*d]; S [H, d, d] at ``s_off`` of the request's row of ``state``."""
+    T = r.shape[0]
+    assert r.dtype == k.dtype == v.dtype == w.dtype == out.dtype == torch.float32
+    assert r.shape == k.shape == v.shape == w.shape == out.shape == (T, H * d)
+    assert r.stride(0) == k.stride(0) == v.stride(0) and r.stride(1) == k.stride(1) == v.stride(1) == 1
+    assert u.shape == (H, d) and u.dtype == torch.float32 and state.dtype == torch.float32
+    _contig(w, "w"); _contig(out, "out"); _contig(u, "u"); _contig(state, "state")
+    _check(library("time_mix").qd_tm_scan(
+        _ptr(r), _ptr(k), _ptr(v), _LL(r.stride(0)), _ptr(w), _ptr(u), _I(H), _I(d), _I(d), _ptr(state),
+        _LL(state.stride(0)), _LL(s_off), _ptr(ctx.cu_tokens), _ptr(ctx.state_slots), _I(ctx.num_requests), _ptr(out),
+        _I(1 if write_state else 0), _stream()), "tm_scan")
+
+
+def tm_finish(o: torch.Tensor, g: torch.Tensor, norm: torch.Tensor, H: int, d: int, eps: float, out_scale: float,
+              out: torch.Tensor, h: torch.Tensor, state: torch.Tensor, prev_off: int, ctx, write_state: bool) -> None:
+    """out[t, head] = o / sqrt(mean(o^2) + eps) * norm * silu(g) * out_scale per head of d values; o float32
+    [T, H*d], g float32 [T, H*d] (rows may be strided), norm float32 [H*d]; out [T, H*d] (rows may be strided).  The
+    last token of every portion leaves its row of h [T, D] as the request's kept input at ``prev_off``."""
+    T = o.shape[0]
+    assert o.dtype == g.dtype == norm.dtype == torch.float32 and o.shape == g.shape == out.shape == (T, H * d)
+    assert g.stride(1) == 1 and out.stride(1) == 1 and norm.numel() == H * d
+    _contig(o, "o"); _contig(h, "h"); _contig(state, "state")
+    _check(library("time_mix").qd_tm_finish(
+        _ptr(o), _ptr(g), _LL(g.stride(0)), _ptr(norm), _I(T), _I(H), _I(d), _F(eps), _F(out_scale), _ptr(out),
+        _I(dtype_code(out.dtype)), _LL(out.stride(0)), _ptr(h), _I(dtype_code(h.dtype)), _I(h.shape[1]), _ptr(state),
+        _LL(state.stride(0)), _LL(prev_off), _ptr(ctx.token_request), _ptr(ctx.cu_tokens), _ptr(ctx.state_slots),
+        _I(1 if write_state else 0), _stream()), "tm_finish")
 
 
 # ------------------------------------------------------------------ the layers of a prompt step from native code

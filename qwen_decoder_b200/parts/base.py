@@ -61,41 +61,47 @@ class ResidualStream:
         self.delta2: Optional[torch.Tensor] = None          # a second pending branch (plain)
         self.delta_gate: Optional[torch.Tensor] = None      # float32 logits [T, D]: the pending branch joins times their sigmoid
         self.delta_gate_bias: Optional[torch.Tensor] = None  # float32 [D]: added to every row of the logits first
+        self.delta_mult = 1.0                               # a constant on what is pending (both outputs of a pair)
         self.origin: Optional[torch.Tensor] = None          # the embedding output, kept when a block reads it again
 
     def push(self, delta: torch.Tensor, scale: Optional[torch.Tensor] = None, unit=None,
-             gate: Optional[torch.Tensor] = None, gate_bias: Optional[torch.Tensor] = None) -> None:
+             gate: Optional[torch.Tensor] = None, gate_bias: Optional[torch.Tensor] = None, mult: float = 1.0) -> None:
         """Hand over a branch output (times ``scale`` along D, or times sigmoid(``gate`` + ``gate_bias``) element by
-        element, if given); what is still pending is added first."""
+        element, if given; times the constant ``mult``); what is still pending is added first."""
         self.flush()
+        if mult != 1.0 and (scale is not None or gate is not None):
+            raise ValueError("a constant on a branch that has a layer scale or a gate is not supported")
+        self.delta_mult = float(mult)
         self.delta = delta
         self.delta_scale = scale
         self.delta_unit = unit
         self.delta_gate = gate
         self.delta_gate_bias = gate_bias
 
-    def push_pair(self, delta: torch.Tensor, delta2: torch.Tensor) -> None:
-        """Hand over the outputs of two branches that read the same x."""
+    def push_pair(self, delta: torch.Tensor, delta2: torch.Tensor, mult: float = 1.0) -> None:
+        """Hand over the outputs of two branches that read the same x (both times the constant ``mult``)."""
         self.flush()
-        self.delta, self.delta2 = delta, delta2
+        self.delta, self.delta2, self.delta_mult = delta, delta2, float(mult)
 
     def pending(self):
-        """The pending outputs as (tensor, unit) pairs, for a kernel that adds up to two of them."""
+        """The pending outputs as (tensor, unit, constant) triples, for a kernel that adds up to two of them."""
         out = []
         if self.delta is not None:
-            out.append((self.delta, self.delta_unit))
+            out.append((self.delta, self.delta_unit, self.delta_mult))
         if self.delta2 is not None:
-            out.append((self.delta2, None))
+            out.append((self.delta2, None, self.delta_mult))
         return out
 
     def clear(self) -> None:
         self.delta = self.delta_scale = self.delta_unit = self.delta2 = self.delta_gate = None
         self.delta_gate_bias = None
+        self.delta_mult = 1.0
 
     def settle(self, gated_ok: bool = False) -> None:
         """Add what only ``flush`` can add (a second output, a unit-normalised one, and -- unless the caller's own
         kernel takes it, ``gated_ok`` -- a gated one); a plain pending delta stays."""
-        if self.delta2 is not None or self.delta_unit is not None or (self.delta_gate is not None and not gated_ok):
+        if self.delta2 is not None or self.delta_unit is not None or self.delta_mult != 1.0 or \
+                (self.delta_gate is not None and not gated_ok):
             self.flush()
 
     def flush(self) -> None:
@@ -105,7 +111,7 @@ class ResidualStream:
             if self.delta2 is not None or self.delta_unit is not None or self.delta_scale is not None:
                 raise ValueError("a gated branch beside a second, a scaled or a unit-normalised one is not supported")
             kernels.gated_add_norm(self.x, self.delta, self.delta_gate, gate_bias=self.delta_gate_bias)
-        elif self.delta2 is None and self.delta_unit is None:
+        elif self.delta2 is None and self.delta_unit is None and self.delta_mult == 1.0:
             kernels.residual_add(self.x, self.delta, self.delta_scale)
         else:
             if self.delta_scale is not None:

@@ -124,6 +124,10 @@ class ParallelSideBlock(Block):
     own slice.  Tensors of the block: ``<prefix>side.gate`` [side_dim, D], ``<prefix>side.proj`` [D, side_dim],
     ``<prefix>side.norm`` [D].  With ``side_dim`` = 0 the block ends after the two branches.
 
+    ``shared_norm``: there is one norm and both branches read its output, x += mixer(h) + feed_forward(h) with
+    h = norm1(x).  ``mult``: a constant m on everything the layer adds, x += m (mixer + feed_forward) and
+    x += m y / sqrt(mean(y^2) + eps) * ws.
+
     Nothing is added to the residual sum by a kernel of its own where the next kernel can do it: the branch outputs
     wait on the stream for the kernel that needs the new sum (the side input's, which also writes the rounded copy the
     gate product reads), and the side output waits, to be unit-normalised and added, for the next layer's norms.  When
@@ -132,11 +136,13 @@ class ParallelSideBlock(Block):
 
     def __init__(self, mixer: Mixer, feed_forward, norms: Dict[str, Norm], size: int, eps: float = 1e-6,
                  side_dim: int = 0, side_index: int = 0, side_table: str = "side.embed", side_table_shape=None,
-                 prefix: str = ""):
-        if "input" not in norms or (feed_forward is not None and "post_mixer" not in norms):
+                 prefix: str = "", shared_norm: bool = False, mult: float = 1.0):
+        if "input" not in norms or (feed_forward is not None and not shared_norm and "post_mixer" not in norms):
             raise ValueError("parallel_side block needs the norms 'input' and, with a feed-forward, 'post_mixer'")
         self.mixer, self.feed_forward = mixer, feed_forward
-        self.norm1, self.norm2 = norms["input"], norms.get("post_mixer") if feed_forward is not None else None
+        self.shared_norm, self.mult = bool(shared_norm), float(mult)
+        self.norm1 = norms["input"]
+        self.norm2 = norms.get("post_mixer") if feed_forward is not None and not shared_norm else None
         self.size, self.eps, self.prefix = size, float(eps), prefix
         self.side_dim, self.side_index, self.side_table = int(side_dim), int(side_index), side_table
         self.side_table_shape = tuple(side_table_shape) if side_table_shape else None
@@ -170,10 +176,11 @@ class ParallelSideBlock(Block):
             self.side_rows = source.get(self.side_table)[:, lo:lo + self.side_dim].to(device=device, dtype=dtype).contiguous()
 
     def forward(self, stream: ResidualStream, ctx, cache) -> None:
-        from .norm import TanhNorm
+        from .norm import RMSNorm, TanhNorm
         T, dev = stream.x.shape[0], stream.x.device
         n1, n2 = self.norm1, self.norm2
-        if type(n1) is TanhNorm and (n2 is None or type(n2) is TanhNorm) and stream.delta_scale is None:
+        if type(n1) in (TanhNorm, RMSNorm) and (n2 is None or type(n2) in (TanhNorm, RMSNorm)) and \
+                stream.delta_scale is None and stream.delta_gate is None:
             h1 = torch.empty((T, self.size), dtype=self.dtype, device=dev)
             h2 = torch.empty((T, self.size), dtype=self.dtype, device=dev) if n2 is not None else None
             kernels.add_tanh_norm(stream.x, stream.pending(),
@@ -184,9 +191,9 @@ class ParallelSideBlock(Block):
             h2 = n2.forward(stream, self.dtype) if n2 is not None else None
         a = self.mixer.forward(h1, ctx, cache)
         if self.feed_forward is not None:
-            stream.push_pair(a, self.feed_forward.forward(h2, ctx))
+            stream.push_pair(a, self.feed_forward.forward(h1 if self.shared_norm else h2, ctx), mult=self.mult)
         else:
-            stream.push(a)
+            stream.push(a, mult=self.mult)
         if not self.side_dim:
             return
         # the new sum, and its copy in the engine's dtype for the gate product, in one launch
@@ -195,7 +202,7 @@ class ParallelSideBlock(Block):
         stream.clear()
         g = torch.empty((T, self.side_dim), dtype=self.dtype, device=dev)
         kernels.token_gate(self.gate.forward(xr, out_dtype=torch.float32), self.side_rows, ctx.tokens, g)
-        stream.push(self.proj.forward_partial(g), unit=(self.side_norm, self.eps))
+        stream.push(self.proj.forward_partial(g), unit=(self.side_norm, self.eps), mult=self.mult)
 
 
 @register_part("block", "pre_norm_gated")

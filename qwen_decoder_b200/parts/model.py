@@ -23,7 +23,7 @@ from .linear import Linear
 # importing the part modules registers them
 from . import attention as _attention, block as _block, mlp as _mlp, norm as _norm, rotary as _rotary  # noqa: F401
 from . import latent_attention as _latent, mamba2 as _mamba2, moe as _moe, sink_attention as _sink  # noqa: F401
-from . import diff_attention as _diff  # noqa: F401
+from . import diff_attention as _diff, masked_attention as _masked, side_by_side as _side, time_mix as _tmix  # noqa: F401
 
 
 class DecoderModel:
@@ -38,13 +38,8 @@ class DecoderModel:
         for ls in spec.layers:
             mixer = None                # a block that only works on the residual sum has no mixer
             if ls.mixer is not None:
-                mp = dict(ls.mixer.params)
+                mp = self._with_positions(ls.mixer.params, ls.prefix)
                 mp["prefix"] = ls.prefix + mp.get("prefix", "")
-                if "position" in mp:
-                    pname = mp["position"]
-                    if pname is not None and pname not in self.positions:
-                        raise ValueError(f"layer {ls.prefix!r}: unknown position encoding {pname!r}")
-                    mp["position"] = self.positions[pname] if pname is not None else None
                 mixer = create_part("mixer", ls.mixer.name, **mp)
             ff = None
             if ls.feed_forward is not None:
@@ -81,6 +76,19 @@ class DecoderModel:
         self.native_prompt = None    # parts.native_prompt.NativePrompt once bound, if the parts allow it
         self.dtype: Optional[torch.dtype] = None
         self.device: Optional[torch.device] = None
+
+    def _with_positions(self, params, where: str) -> dict:
+        """A mixer's parameters with the name of its position encoding replaced by the part itself; a mixer made of
+        several (``branches``) has each branch's parameters treated alike."""
+        mp = dict(params)
+        if "position" in mp:
+            pname = mp["position"]
+            if pname is not None and pname not in self.positions:
+                raise ValueError(f"layer {where!r}: unknown position encoding {pname!r}")
+            mp["position"] = self.positions[pname] if pname is not None else None
+        if "branches" in mp:
+            mp["branches"] = [dict(b, params=self._with_positions(b["params"], where)) for b in mp["branches"]]
+        return mp
 
     # ---- tensors ---------------------------------------------------------
     def tensor_specs(self) -> List[TensorSpec]:
@@ -121,7 +129,9 @@ class DecoderModel:
         out = list(self.positions.values())
         for layer in self.layers:
             out.append(layer)
-            out += list(layer.parts()) if hasattr(layer, "parts") else []
+            for part in (list(layer.parts()) if hasattr(layer, "parts") else []):
+                out.append(part)
+                out += list(part.parts()) if hasattr(part, "parts") else []      # a mixer made of several
         out.append(self.final_norm)
         return out
 

@@ -45,6 +45,10 @@ class RMSNorm(Norm):
     def native_params(self) -> Optional[dict]:
         return {"kind": "rmsnorm", "weight": self.weight, "eps": self.eps, "size": self.size}
 
+    def launch_params(self, out: torch.Tensor):
+        """This norm as the kernel that adds up to two pending outputs takes it."""
+        return ("rms", self.weight, self.eps, out)
+
     def forward(self, stream: ResidualStream, out_dtype: torch.dtype,
                 rows: Optional[torch.Tensor] = None) -> torch.Tensor:
         stream.settle(gated_ok=True)

@@ -11,6 +11,11 @@ and the rotation is fused with the cache write (``csrc/elementwise.cu``).
 c(t) = rotary_dim * ln(original / (2 pi t)) / (2 ln base), lo = max(floor(c(fast)), 0), hi = min(ceil(c(slow)),
 rotary_dim - 1) and r_p = clamp((p - lo) / max(hi - lo, 0.001), 0, 1), pair p turns at
 theta_p / factor * r_p + theta_p * (1 - r_p), and every cosine and sine is multiplied by 0.1 ln(factor) + 1.
+
+``scaling`` with ``kind`` = "bands" (keys factor, low, high, original) stretches band by band instead: with the
+wavelength l_p = 2 pi / theta_p, pair p keeps theta_p where l_p < original / high, turns at theta_p / factor where
+l_p > original / low, and between the two at (1 - s) theta_p / factor + s theta_p with
+s = (original / l_p - low) / (high - low); cosines and sines keep their size.
 """
 from __future__ import annotations
 
@@ -36,10 +41,19 @@ class Rotary(PositionEncoding):
         self.base = float(base)
         self.pairing = pairing
         self.pairing_code = PAIRING_CODES[pairing]
+        self.scaling_kind = None
         if scaling is not None:
-            scaling = {k: float(scaling[k]) for k in ("factor", "original", "fast", "slow")}
-            if scaling["factor"] <= 0 or scaling["original"] <= 0 or scaling["fast"] <= 0 or scaling["slow"] <= 0:
-                raise ValueError("rotary scaling: factor, original, fast and slow must be positive")
+            self.scaling_kind = scaling.get("kind", "ramp")
+            if self.scaling_kind == "bands":
+                scaling = {k: float(scaling[k]) for k in ("factor", "original", "low", "high")}
+                if min(scaling.values()) <= 0 or scaling["high"] == scaling["low"]:
+                    raise ValueError("rotary scaling: factor, original, low and high must be positive, low and high unequal")
+            elif self.scaling_kind == "ramp":
+                scaling = {k: float(scaling[k]) for k in ("factor", "original", "fast", "slow")}
+                if scaling["factor"] <= 0 or scaling["original"] <= 0 or scaling["fast"] <= 0 or scaling["slow"] <= 0:
+                    raise ValueError("rotary scaling: factor, original, fast and slow must be positive")
+            else:
+                raise ValueError(f"rotary scaling: kind must be 'ramp' or 'bands', got {self.scaling_kind!r}")
         self.scaling = scaling
         self.cos: Optional[torch.Tensor] = None
         self.sin: Optional[torch.Tensor] = None
@@ -48,7 +62,15 @@ class Rotary(PositionEncoding):
         p = torch.arange(self.rotary_dim // 2, dtype=torch.float64)
         inv_freq = 1.0 / torch.pow(torch.tensor(self.base, dtype=torch.float64), 2.0 * p / self.rotary_dim)
         magnitude = 1.0
-        if self.scaling is not None:
+        if self.scaling_kind == "bands":
+            import math
+            sc = self.scaling
+            wavelength = 2.0 * math.pi / inv_freq
+            blend = (sc["original"] / wavelength - sc["low"]) / (sc["high"] - sc["low"])
+            between = (1.0 - blend) * inv_freq / sc["factor"] + blend * inv_freq
+            inv_freq = torch.where(wavelength < sc["original"] / sc["high"], inv_freq,
+                                   torch.where(wavelength > sc["original"] / sc["low"], inv_freq / sc["factor"], between))
+        elif self.scaling is not None:
             import math
             sc = self.scaling
             turns = lambda t: self.rotary_dim * math.log(sc["original"] / (2.0 * math.pi * t)) / (2.0 * math.log(self.base))

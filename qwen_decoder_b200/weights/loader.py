@@ -37,10 +37,16 @@ class WeightError(ValueError):
 class TensorSpec:
     """A tensor a part needs: full name, shape, and how random weights fill it
     (``normal``: N(0, std); ``around_one``: 1 + N(0, norm_std), for norm scales; ``around_zero``: N(0, norm_std),
-    for scales stored as their distance from one; ``uniform:lo:hi``)."""
+    for scales stored as their distance from one; ``uniform:lo:hi``).  A size of -1 in ``shape`` is one that only the
+    stored tensor gives (the part reads it when it binds); ``default_shape`` is what random weights use then."""
     name: str
     shape: Tuple[int, ...]
     init: str = "normal"
+    default_shape: Optional[Tuple[int, ...]] = None
+
+
+def shape_fits(want: Tuple[int, ...], found: Tuple[int, ...]) -> bool:
+    return len(want) == len(found) and all(w == f or w == -1 for w, f in zip(want, found))
 
 
 def storage_dtype(dt: torch.dtype) -> torch.dtype:
@@ -70,7 +76,7 @@ def check_tensors(specs: Iterable[TensorSpec], found: Mapping[str, Tuple[int, ..
         warnings.warn(f"weights{' in ' + where if where else ''}: tensors present but not used by this "
                       f"configuration: {', '.join(ignored)}")
     unexpected = sorted(n for n in found if n not in want and n not in ignorable)
-    wrong = sorted((n, want[n], tuple(found[n])) for n in want if n in found and tuple(found[n]) != want[n])
+    wrong = sorted((n, want[n], tuple(found[n])) for n in want if n in found and not shape_fits(want[n], tuple(found[n])))
     if not (missing or unexpected or wrong):
         return
     lines = [f"weights{' in ' + where if where else ''} do not fit the model:"]

@@ -27,7 +27,12 @@ def random_tensor(spec: TensorSpec, seed: int, dtype=torch.bfloat16, device="cpu
                   std: float = 0.02, norm_std: float = 0.1) -> torch.Tensor:
     g = torch.Generator(device=device)
     g.manual_seed(_tensor_seed(seed, spec.name))
-    t = torch.empty(spec.shape, dtype=torch.float32, device=device)
+    shape = spec.shape
+    if any(n == -1 for n in shape):
+        if spec.default_shape is None:
+            raise ValueError(f"tensor {spec.name!r}: a size that only a stored tensor gives, and no default for random weights")
+        shape = spec.default_shape
+    t = torch.empty(shape, dtype=torch.float32, device=device)
     if spec.init == "around_one":
         t.normal_(0.0, norm_std, generator=g).add_(1.0)
     elif spec.init == "around_zero":
