@@ -341,6 +341,51 @@ def solopel_configs(size, layers=None):
     return solopel, veterax
 
 
+# ---- Fogurax beside Veterax at equal layer sizes --------------------------------------------------------------------
+# Eight layers: convolved attention + dense feed-forward, block-masked attention + routed experts, convolved attention +
+# dense, windowed attention beside the recurrent mixer + routed experts, twice.  Heads of 128 with values of 128, windows
+# and blocks of 1,024 positions, recurrent heads of 64 (width / 64 of them), the token input of 256.  The other model:
+# Veterax (the closest one: parallel layers, a token input, attention with values of their own size, routed experts with a
+# shared one) with the same width, depth, heads, expert sizes and vocabulary.
+FOGURAX_SIZES = {
+    "S": dict(width=2048, vocab=32000, heads=(16, 2), dim=128, vdim=128, span=1024, ff=5632, rank=64,
+              moe=dict(experts=64, top=6, ff=1408, shared=2816)),
+    "M": dict(width=4096, vocab=32000, heads=(32, 8), dim=128, vdim=128, span=1024, ff=11008, rank=64,
+              moe=dict(experts=32, top=4, ff=2048, shared=4096)),
+}
+
+
+def fogurax_configs(size, layers=None):
+    from qwen_decoder_b200.config import config_from_dict
+    z = FOGURAX_SIZES[size]
+    H, G = z["heads"]
+    m, d = z["moe"], z["dim"]
+    base = {"heads": H, "kv_heads": G, "dim": d, "vdim": z["vdim"], "scale": d ** -0.5}
+    conv = {"type": "attention", "mixer": dict(base, conv=4, rot={"base": 500000.0, "dims": d // 2, "scaling": {
+        "factor": 8.0, "low": 1.0, "high": 4.0, "original": 8192}})}
+    block = {"type": "attention_2", "mixer": dict(base, mask={"size": z["span"]}, rot={"base": 500000.0, "dims": d // 2, "scaling": {
+        "factor": 4.0, "original": 8192, "fast": 32.0, "slow": 1.0}})}
+    both = {"type": "parallel", "mixer": {"left": dict(base, mask={"size": z["span"]}, rot={"base": 1000000.0, "dims": d}),
+                                          "right": {"heads": z["width"] // 64, "dim": 64, "rank": z["rank"]},
+                                          "left_scale": 1.2, "right_scale": 1.1}}
+    moe = {"kind": "moe", "expert": {"ff": m["ff"]}, "router": {"experts": m["experts"], "top": m["top"]},
+           "shared": {"ff": m["shared"]}}
+    dense = {"kind": "dense", "ff": z["ff"]}
+    eight = [dict(conv, mlp=dense), dict(block, mlp=moe), dict(conv, mlp=dense), dict(both, mlp=moe)] * 2
+    if layers:                  # fewer layers of the same sizes (a capture under a profiler holds fewer weights)
+        eight = eight[:max(1, layers)]
+    fogurax = config_from_dict({"architecture": "Fogurax", "vocab": z["vocab"], "width": z["width"], "norm": {"eps": 1e-5},
+                                "residual_mult": 0.5, "token_side": {"dim": 256}, "layers": eight})
+    vmix = {"heads": H, "kv_heads": G, "dim": d, "vdim": z["vdim"], "scale": d ** -0.5,
+            "rot": {"base": 1000000.0, "dims": d}}
+    vmlp = {"kind": "moe", "expert": {"ff": m["ff"], "limit": 7.0}, "router": {"experts": m["experts"], "identity": 0,
+            "top": m["top"]}, "shared": {"ff": m["shared"], "limit": 7.0}}
+    veterax = config_from_dict({"architecture": "Veterax", "vocab": z["vocab"], "width": z["width"], "norm": {"eps": 1e-5},
+                                "token_side": {"dim": 256},
+                                "layers": [{"type": "attention", "mixer": vmix, "mlp": vmlp} for _ in range(len(eight))]})
+    return fogurax, veterax
+
+
 def hybrid_bench(args, label="hybrid", configs=None, other="dense"):
     """``--micro hybrid`` (and ``--micro veterax``, which passes its own pair of models): decode steps (batch 1, 8, 64 at ``--context``) and a prompt of ``--prefill-tokens`` tokens, for the
     hybrid design and for the dense decoder at equal sizes; one JSON line.  ``--only hybrid|dense`` and ``--phase`` narrow it
@@ -490,6 +535,8 @@ def micro(args):
         return hybrid_bench(args, "veterax", lambda size: veterax_configs(size, args.veterax_layers))
     if args.micro == "solopel":
         return hybrid_bench(args, "solopel", lambda size: solopel_configs(size, args.veterax_layers), other="veterax")
+    if args.micro == "fogurax":
+        return hybrid_bench(args, "fogurax", lambda size: fogurax_configs(size, args.veterax_layers), other="veterax")
     if args.micro == "latent_attend":
         return latent_attend_micro(args)
     """One kernel alone: W-streaming contraction, decode attention or prefill attention at the 3B sizes."""
@@ -741,7 +788,7 @@ def main():
     ap.add_argument("--no-e2e", action="store_true")
     ap.add_argument("--timeline", action="store_true",
                     help="with --micro prefill_attention: print the kernel's own time stamps of one CTA (microseconds) to stderr")
-    ap.add_argument("--micro", default=None, choices=["gemm", "decode_attention", "decode_attention_rope", "prefill_attention", "serve", "mixed_step", "hybrid", "latent_attend", "veterax", "solopel"],
+    ap.add_argument("--micro", default=None, choices=["gemm", "decode_attention", "decode_attention_rope", "prefill_attention", "serve", "mixed_step", "hybrid", "latent_attend", "veterax", "solopel", "fogurax"],
                     help="time one kernel alone at the 3B shape (for profiles/), or with 'serve' a whole run of "
                          "--batch requests (--context prompt tokens, --steps new tokens each) through the entry "
                          "point; print one JSON line and exit")
