@@ -42,7 +42,9 @@ struct QkvPrep {
   void* q_out; int q_dtype; void* kv; int kv_dtype; const int* slot_map; int page_size, write_kv;
 };
 
-__global__ void __launch_bounds__(QP_THREADS)
+// NP: pairs of a head that a lane holds (d <= 64 NP); the CTA's threads (a multiple of 32) share a token's channels.
+template <int NP>
+__global__ void __launch_bounds__(1024)
 qkv_prep_kernel(QkvPrep a) {
   pdl_launch_dependents();
   pdl_wait();
@@ -56,7 +58,7 @@ qkv_prep_kernel(QkvPrep a) {
   float* kept = (a.taps > 1) ? a.state + (size_t)a.slots[r] * a.state_stride + a.state_off : nullptr;
   const int first = a.cu_tokens[r];
   float ssq = 0.f, ssk = 0.f;
-  for (int c = tid; c < C; c += QP_THREADS) {
+  for (int c = tid; c < C; c += blockDim.x) {
     const float y = a.taps > 0 ? short_conv_at(a.u, a.ld, C, a.taps, a.conv_w, kept, first, t, c)
                                : a.u[(size_t)t * a.ld + c];
     row[c] = y;
@@ -71,7 +73,7 @@ qkv_prep_kernel(QkvPrep a) {
   __syncthreads();
   // every request brings one token: channel c's kept inputs were read by this thread alone, which now moves them on
   if (a.advance)
-    for (int c = tid; c < C; c += QP_THREADS) short_conv_advance(a.u, a.ld, C, a.taps, kept, t, t + 1, c);
+    for (int c = tid; c < C; c += blockDim.x) short_conv_advance(a.u, a.ld, C, a.taps, kept, t, t + 1, c);
 
   size_t page = 0, off = 0;
   if (a.write_kv) {
@@ -82,16 +84,16 @@ qkv_prep_kernel(QkvPrep a) {
   const size_t page_elems = (size_t)G * a.page_size * (d + vd);
   const int pos = a.positions[t];
   const int half = a.rotary_dim / 2, pairs = d / 2;
-  for (int s = warp; s < H + G; s += QP_THREADS / 32) {
+  for (int s = warp; s < H + G; s += blockDim.x >> 5) {
     const bool is_q = s < H;
     if (!is_q && !a.write_kv) continue;
     const int base = is_q ? s * d : nq + (s - H) * d;           // the head's first channel in the row
     const float* w = a.norm_mode == 1 ? (is_q ? a.wq + s * d : a.wk + (s - H) * d) : nullptr;
     const float f = is_q ? fq : fk;
-    float x[QP_MAX_D / 64], y[QP_MAX_D / 64];
+    float x[NP], y[NP];
     float ss = 0.f;
 #pragma unroll
-    for (int i = 0; i < QP_MAX_D / 64; i++) {
+    for (int i = 0; i < NP; i++) {
       const int j = lane + 32 * i;
       x[i] = y[i] = 0.f;
       if (j >= pairs) continue;
@@ -105,11 +107,11 @@ qkv_prep_kernel(QkvPrep a) {
     if (a.norm_mode == 2 && !a.norm_after) {
       const float fh = 1.0f / sqrtf(warp_sum(ss) / (float)d + a.eps);
 #pragma unroll
-      for (int i = 0; i < QP_MAX_D / 64; i++) { x[i] *= fh; y[i] *= fh; }
+      for (int i = 0; i < NP; i++) { x[i] *= fh; y[i] *= fh; }
     }
     ss = 0.f;
 #pragma unroll
-    for (int i = 0; i < QP_MAX_D / 64; i++) {
+    for (int i = 0; i < NP; i++) {
       const int j = lane + 32 * i;
       if (j < half) {
         const float c = a.cos_t[(size_t)pos * half + j], sn = a.sin_t[(size_t)pos * half + j];
@@ -125,7 +127,7 @@ qkv_prep_kernel(QkvPrep a) {
     void* out = is_q ? a.q_out : a.kv;
     const int oc = is_q ? a.q_dtype : a.kv_dtype;
 #pragma unroll
-    for (int i = 0; i < QP_MAX_D / 64; i++) {
+    for (int i = 0; i < NP; i++) {
       const int j = lane + 32 * i;
       if (j >= pairs) continue;
       int ia, ib;
@@ -136,7 +138,7 @@ qkv_prep_kernel(QkvPrep a) {
   }
   if (!a.write_kv) return;
   const size_t vdst = page * page_elems + (size_t)G * a.page_size * d;
-  for (int c = tid; c < G * vd; c += QP_THREADS) {
+  for (int c = tid; c < G * vd; c += blockDim.x) {
     const int g = c / vd, i = c - g * vd;
     qp_st(a.kv, a.kv_dtype, vdst + ((size_t)g * a.page_size + off) * vd + i, row[nq + nk + c]);
   }
@@ -175,14 +177,18 @@ extern "C" int qd_qkv_prep(const float* u, long long ld, int T, int n_requests, 
   if (smem > 200 * 1024) return QD_ERR_UNSUPPORTED;
   static size_t raised = 48 * 1024;
   if (smem > raised) {
-    cudaFuncSetAttribute(qkv_prep_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    cudaFuncSetAttribute(qkv_prep_kernel<2>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    cudaFuncSetAttribute(qkv_prep_kernel<QP_MAX_D / 64>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
     raised = smem;
   }
+  // few tokens: a token's channels and heads are shared among more threads (a decode step waits for its longest CTA)
+  const int threads = T <= 128 ? (C >= 4096 ? 1024 : 512) : QP_THREADS;
   const int advance = update_state && taps > 1 && T == n_requests;     // single tokens, one per request
   QkvPrep a = {u, ld, H, G, d, vd, taps, conv_w, state, state_stride, state_off, token_req, cu_tokens, slots, advance,
                norm_mode, norm_after, wq, wk, eps, rotary_dim, pairing, cos_t, sin_t, positions, q_out, q_dtype, kv,
                kv_dtype, slot_map, page_size, write_kv};
-  qd_launch(qkv_prep_kernel, dim3(T), dim3(QP_THREADS), smem, stream, a);
+  if (d <= 128) qd_launch(qkv_prep_kernel<2>, dim3(T), dim3(threads), smem, stream, a);
+  else qd_launch(qkv_prep_kernel<QP_MAX_D / 64>, dim3(T), dim3(threads), smem, stream, a);
   if (update_state && taps > 1 && !advance)
     qd_launch(qkv_prep_state_kernel, dim3((unsigned)((C + 255) / 256), n_requests), dim3(256), 0, stream, u, ld, (int)C,
               taps, state, state_stride, state_off, cu_tokens, slots);

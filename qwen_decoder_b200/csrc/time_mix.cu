@@ -45,44 +45,64 @@ extern "C" int qd_tm_shift_mix(const void* h, int dtype, int T, int D, const flo
                                long long state_stride, long long prev_off, const int* token_req, const int* cu_tokens,
                                const int* slots, void* out, cudaStream_t stream) {
   if (T <= 0) return 0;
-  if (T > 65535 || D <= 0 || n_mix <= 0 || !state) return QD_ERR_UNSUPPORTED;
+  if (T > 65535 || D <= 0 || n_mix <= 0 || !state) return QD_ERR_UNSUPPORTED;     // a step's tokens are far fewer
   qd_launch(tm_shift_mix_kernel, dim3((D + 255) / 256, T), dim3(256), 0, stream, h, dtype, T, D, mu, n_mix, state,
             state_stride, prev_off, token_req, cu_tokens, slots, out);
   return qd_last_error();
 }
 
 // ---------------------------------------------------------------------------------------------------------- decay
-// grid (ceil(C / 128), T).  a float32 [T, lda] (the first R columns); w2 [C, R] (``w_dtype``); w0 float32 [C].
+// grid (ceil(C / 128), ceil(T / TD_TOKENS)), 128 threads.  a float32 [T, lda] (the first R columns); w2t [R, C]
+// (``w_dtype``; the transpose of the stored [C, R], so that neighbouring threads read neighbouring numbers);
+// w0 float32 [C].  A CTA keeps its 128 channels' columns of w2t in shared memory (float32) for its TD_TOKENS tokens.
+#define TD_TOKENS 16
+
 __global__ void __launch_bounds__(128)
-tm_decay_kernel(const float* __restrict__ a, long long lda, int R, const void* __restrict__ w2, int w_dtype,
+tm_decay_kernel(const float* __restrict__ a, long long lda, int T, int R, const void* __restrict__ w2t, int w_dtype,
                 const float* __restrict__ w0, int C, float* __restrict__ out) {
   pdl_launch_dependents();
+  extern __shared__ float td_sm[];                    // [R][128] weights, then [TD_TOKENS][R] tanh values
+  float* ws = td_sm;
+  float* th = td_sm + (size_t)R * 128;
+  const int c = blockIdx.x * 128 + threadIdx.x;
+  const int t0 = blockIdx.y * TD_TOKENS, nt = min(TD_TOKENS, T - t0);
+  for (int i = 0; i < R; i++) ws[i * 128 + threadIdx.x] = c < C ? tm_ld(w2t, w_dtype, (size_t)i * C + c) : 0.f;
+  const float b = c < C ? w0[c] : 0.f;
   pdl_wait();
-  extern __shared__ float th[];
-  const int t = blockIdx.y;
-  for (int i = threadIdx.x; i < R; i += blockDim.x) th[i] = tanhf(a[(size_t)t * lda + i]);
+  for (int e = threadIdx.x; e < nt * R; e += 128) {
+    const int tt = e / R, i = e - tt * R;
+    th[e] = tanhf(a[(size_t)(t0 + tt) * lda + i]);
+  }
   __syncthreads();
-  const int c = blockIdx.x * blockDim.x + threadIdx.x;
   if (c >= C) return;
-  float z = w0[c];
-  for (int i = 0; i < R; i++) z = fmaf(th[i], tm_ld(w2, w_dtype, (size_t)c * R + i), z);
-  out[(size_t)t * C + c] = expf(-expf(z));
+  for (int tt = 0; tt < nt; tt++) {
+    float z = b;
+    for (int i = 0; i < R; i++) z = fmaf(th[tt * R + i], ws[i * 128 + threadIdx.x], z);
+    out[(size_t)(t0 + tt) * C + c] = expf(-expf(z));
+  }
 }
 
-extern "C" int qd_tm_decay(const float* a, long long lda, int T, int R, const void* w2, int w_dtype, const float* w0,
+extern "C" int qd_tm_decay(const float* a, long long lda, int T, int R, const void* w2t, int w_dtype, const float* w0,
                            int C, float* out, cudaStream_t stream) {
   if (T <= 0) return 0;
-  if (T > 65535 || R <= 0 || R > 8192 || C <= 0) return QD_ERR_UNSUPPORTED;
-  qd_launch(tm_decay_kernel, dim3((C + 127) / 128, T), dim3(128), (size_t)R * sizeof(float), stream, a, lda, R, w2,
-            w_dtype, w0, C, out);
+  const size_t smem = ((size_t)R * 128 + (size_t)TD_TOKENS * R) * sizeof(float);
+  if (R <= 0 || C <= 0 || smem > 200 * 1024 || (T + TD_TOKENS - 1) / TD_TOKENS > 65535) return QD_ERR_UNSUPPORTED;
+  static size_t raised = 48 * 1024;
+  if (smem > raised) {
+    cudaFuncSetAttribute(tm_decay_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    raised = smem;
+  }
+  qd_launch(tm_decay_kernel, dim3((C + 127) / 128, (T + TD_TOKENS - 1) / TD_TOKENS), dim3(128), smem, stream, a, lda, T,
+            R, w2t, w_dtype, w0, C, out);
   return qd_last_error();
 }
 
 // ----------------------------------------------------------------------------------------------------------- scan
 // grid (ceil(dv / 16), H, requests), 256 threads: thread (x = tid & 15, column = tid >> 4) keeps NI elements
-// S[x + 16 n, column] of the state in registers.  r, k, w of TM_ROUND tokens arrive in shared memory per round; a
-// token then costs NI x 4 FMAs a thread and a reduction over the 16 threads of a column.
-#define TM_ROUND 8
+// S[x + 16 n, column] of the state in registers.  r, k, w of TM_ROUND tokens arrive in shared memory per round (the
+// next round's are fetched into registers while this round is computed, so a round never waits for memory but at the
+// start); a token then costs NI x 4 FMAs a thread and a reduction over the 16 threads of a column.
+#define TM_ROUND 16
 
 template <int NI>
 __global__ void __launch_bounds__(256)
@@ -107,21 +127,36 @@ tm_scan_kernel(const float* __restrict__ r_, const float* __restrict__ k_, const
     s[n] = (live && i < d) ? S[(size_t)i * dv + j] : 0.f;
     uu[n] = i < d ? u_[(size_t)h * d + i] : 0.f;
   }
+  // element e of a round's [TM_ROUND][3][d] operands: this thread fetches e = tid + 256 q, q < PF
+  constexpr int PF = (TM_ROUND * 3 * 16 * NI + 255) / 256;
+  float pf[PF], pv = 0.f;
+  auto fetch = [&](int tb) {
+    const int nt = min(TM_ROUND, t1 - tb);
+#pragma unroll
+    for (int q = 0; q < PF; q++) {
+      const int e = tid + 256 * q;
+      pf[q] = 0.f;
+      if (e < nt * 3 * d) {
+        const int tt = e / (3 * d), rem = e - tt * 3 * d, which = rem / d, i = rem - which * d;
+        const size_t src = (size_t)(tb + tt) * ld + (size_t)h * d + i;
+        pf[q] = which == 0 ? r_[src] : which == 1 ? k_[src] : w_[(size_t)(tb + tt) * H * d + (size_t)h * d + i];
+      }
+    }
+    const int tt = tid >> 4, jj = blockIdx.x * 16 + (tid & 15);
+    pv = (tt < nt && jj < dv) ? v_[(size_t)(tb + tt) * ld + (size_t)h * dv + jj] : 0.f;
+  };
+  fetch(t0);
   for (int tb = t0; tb < t1; tb += TM_ROUND) {
     const int nt = min(TM_ROUND, t1 - tb);
-    __syncthreads();
-    for (int e = tid; e < nt * d; e += 256) {
-      const int tt = e / d, i = e - tt * d;
-      const size_t src = (size_t)(tb + tt) * ld + (size_t)h * d + i;
-      tm_sm[(tt * 3 + 0) * d + i] = r_[src];
-      tm_sm[(tt * 3 + 1) * d + i] = k_[src];
-      tm_sm[(tt * 3 + 2) * d + i] = w_[(size_t)(tb + tt) * H * d + (size_t)h * d + i];
+    __syncthreads();                                  // the round before is computed
+#pragma unroll
+    for (int q = 0; q < PF; q++) {
+      const int e = tid + 256 * q;
+      if (e < nt * 3 * d) tm_sm[e] = pf[q];
     }
-    if (tid < nt * 16) {
-      const int tt = tid >> 4, jj = blockIdx.x * 16 + (tid & 15);
-      vs[tid] = jj < dv ? v_[(size_t)(tb + tt) * ld + (size_t)h * dv + jj] : 0.f;
-    }
+    vs[tid] = pv;
     __syncthreads();
+    if (tb + TM_ROUND < t1) fetch(tb + TM_ROUND);     // in flight while this round is computed
     for (int tt = 0; tt < nt; tt++) {
       const float vj = vs[tt * 16 + jl];
       const float *rs = tm_sm + (tt * 3) * d, *ks = rs + d, *ws = ks + d;
@@ -175,7 +210,7 @@ extern "C" int qd_tm_scan(const float* r, const float* k, const float* v, long l
 }
 
 // --------------------------------------------------------------------------------------------------------- finish
-// grid (T), 256 threads: a warp per head in turn.  o float32 [T, H*dv]; g float32 [T, ldg] gate logits (silu is taken
+// grid (T, ceil(H / 8)), 256 threads: a warp per head.  o float32 [T, H*dv]; g float32 [T, ldg] gate logits (silu is taken
 // here); norm float32 [H*dv]; out rows ``out_stride`` apart in ``out_dtype``.  The last token of a portion copies
 // its row of h [T, D] (``h_dtype``) into the request's state row at ``prev_off``.
 __global__ void __launch_bounds__(256)
@@ -188,7 +223,8 @@ tm_finish_kernel(const float* __restrict__ o, const float* __restrict__ g, long 
   pdl_launch_dependents();
   pdl_wait();
   const int t = blockIdx.x, warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  for (int hd = warp; hd < H; hd += 8) {
+  const int hd = blockIdx.y * 8 + warp;
+  if (hd < H) {
     const size_t base = (size_t)t * H * dv + (size_t)hd * dv;
     float ss = 0.f;
     for (int i = lane; i < dv; i += 32) { const float y = o[base + i]; ss = fmaf(y, y, ss); }
@@ -199,7 +235,7 @@ tm_finish_kernel(const float* __restrict__ o, const float* __restrict__ g, long 
       tm_st(out, out_dtype, (size_t)t * out_stride + (size_t)hd * dv + i, o[base + i] * f * norm[hd * dv + i] * gate);
     }
   }
-  if (!write_state) return;
+  if (!write_state || blockIdx.y != 0) return;
   const int r = token_req[t];
   if (t != cu_tokens[r + 1] - 1) return;
   float* prev = state + (size_t)slots[r] * state_stride + prev_off;
@@ -213,7 +249,8 @@ extern "C" int qd_tm_finish(const float* o, const float* g, long long ldg, const
                             cudaStream_t stream) {
   if (T <= 0) return 0;
   if (H <= 0 || dv <= 0 || !state) return QD_ERR_UNSUPPORTED;
-  qd_launch(tm_finish_kernel, dim3(T), dim3(256), 0, stream, o, g, ldg, norm, H, dv, eps, out_scale, out, out_dtype,
+  if ((H + 7) / 8 > 65535) return QD_ERR_UNSUPPORTED;
+  qd_launch(tm_finish_kernel, dim3(T, (H + 7) / 8), dim3(256), 0, stream, o, g, ldg, norm, H, dv, eps, out_scale, out, out_dtype,
             out_stride, h, h_dtype, D, state, state_stride, prev_off, token_req, cu_tokens, slots, write_state);
   return qd_last_error();
 }

@@ -1380,11 +1380,11 @@ def tm_shift_mix(h: torch.Tensor, mu: torch.Tensor, state: torch.Tensor, prev_of
 
 
 def tm_decay(a: torch.Tensor, w2: torch.Tensor, w0: torch.Tensor, out: torch.Tensor) -> None:
-    """out[t, c] = exp(-exp(w0[c] + sum_r tanh(a[t, r]) w2[c, r])); a float32 [T, R] (rows may be strided), w2 [C, R],
-    w0 float32 [C], out float32 [T, C]."""
+    """out[t, c] = exp(-exp(w0[c] + sum_r tanh(a[t, r]) w2[r, c])); a float32 [T, R] (rows may be strided), w2 [R, C]
+    (the transpose of the stored matrix), w0 float32 [C], out float32 [T, C]."""
     T, R = a.shape
-    C = w2.shape[0]
-    assert a.dtype == torch.float32 and a.stride(1) == 1 and w2.shape == (C, R) and w0.dtype == torch.float32
+    C = w2.shape[1]
+    assert a.dtype == torch.float32 and a.stride(1) == 1 and w2.shape == (R, C) and w0.dtype == torch.float32
     assert w0.numel() == C and out.shape == (T, C) and out.dtype == torch.float32
     _contig(w2, "w2"); _contig(out, "out")
     _check(library("time_mix").qd_tm_decay(_ptr(a), _LL(a.stride(0)), _I(T), _I(R), _ptr(w2), _I(dtype_code(w2.dtype)),

@@ -84,9 +84,10 @@ class TimeMix(Mixer):
         f32 = lambda n: source.get(n).to(device=device, dtype=torch.float32).contiguous()
         self.mu = torch.stack([f32(f"{p}mu.{s}") for s in BLENDS]).contiguous()
         self.w1 = source.get(f"{p}w1{self.sfx}").to(device=device, dtype=dtype).contiguous()
-        self.w2 = source.get(f"{p}w2{self.sfx}").to(device=device, dtype=dtype).contiguous()
-        if self.w1.shape[0] != self.w2.shape[1]:
-            raise ValueError(f"time_mix: {p}w1 has rank {self.w1.shape[0]}, {p}w2 has {self.w2.shape[1]}")
+        # kept as its transpose [R, H*d]: the decay's kernel reads neighbouring channels side by side
+        self.w2 = source.get(f"{p}w2{self.sfx}").to(device=device, dtype=dtype).t().contiguous()
+        if self.w1.shape[0] != self.w2.shape[0]:
+            raise ValueError(f"time_mix: {p}w1 has rank {self.w1.shape[0]}, {p}w2 has {self.w2.shape[0]}")
         self.decay_rank = self.w1.shape[0]
         self.w0, self.u, self.norm = f32(f"{p}w0"), f32(f"{p}u"), f32(f"{p}norm")
 
