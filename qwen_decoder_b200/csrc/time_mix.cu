@@ -112,8 +112,8 @@ tm_scan_kernel(const float* __restrict__ r_, const float* __restrict__ k_, const
                const int* __restrict__ slots, float* __restrict__ out, int write_state) {
   pdl_launch_dependents();
   pdl_wait();
-  extern __shared__ float tm_sm[];                    // [TM_ROUND][3][d] r, k, w; then [TM_ROUND][16] v
-  float* vs = tm_sm + (size_t)TM_ROUND * 3 * d;
+  extern __shared__ float tm_sm[];                    // [TM_ROUND][3][16 NI] r, k, w; then [TM_ROUND][16] v
+  float* vs = tm_sm + (size_t)TM_ROUND * 3 * 16 * NI;
   const int tid = threadIdx.x, x = tid & 15, jl = tid >> 4;
   const int h = blockIdx.y, req = blockIdx.z, j = blockIdx.x * 16 + jl;
   const bool live = j < dv;
@@ -127,17 +127,19 @@ tm_scan_kernel(const float* __restrict__ r_, const float* __restrict__ k_, const
     s[n] = (live && i < d) ? S[(size_t)i * dv + j] : 0.f;
     uu[n] = i < d ? u_[(size_t)h * d + i] : 0.f;
   }
-  // element e of a round's [TM_ROUND][3][d] operands: this thread fetches e = tid + 256 q, q < PF
-  constexpr int PF = (TM_ROUND * 3 * 16 * NI + 255) / 256;
+  // A round's operands in shared memory: [TM_ROUND][3][DP] with DP = 16 NI >= d; places past the portion's end or
+  // past d hold r = 0, k = 0, w = 1 (and v = 0), which leave the state and the sums as they are.  Element
+  // e = tid + 256 q of it is fetched by this thread, q < PF.
+  constexpr int DP = 16 * NI, PF = 3 * NI * TM_ROUND / 16;
   float pf[PF], pv = 0.f;
   auto fetch = [&](int tb) {
     const int nt = min(TM_ROUND, t1 - tb);
 #pragma unroll
     for (int q = 0; q < PF; q++) {
       const int e = tid + 256 * q;
-      pf[q] = 0.f;
-      if (e < nt * 3 * d) {
-        const int tt = e / (3 * d), rem = e - tt * 3 * d, which = rem / d, i = rem - which * d;
+      const int tt = e / (3 * DP), rem = e - tt * 3 * DP, which = rem / DP, i = rem - which * DP;
+      pf[q] = which == 2 ? 1.f : 0.f;
+      if (tt < nt && i < d) {
         const size_t src = (size_t)(tb + tt) * ld + (size_t)h * d + i;
         pf[q] = which == 0 ? r_[src] : which == 1 ? k_[src] : w_[(size_t)(tb + tt) * H * d + (size_t)h * d + i];
       }
@@ -150,32 +152,38 @@ tm_scan_kernel(const float* __restrict__ r_, const float* __restrict__ k_, const
     const int nt = min(TM_ROUND, t1 - tb);
     __syncthreads();                                  // the round before is computed
 #pragma unroll
-    for (int q = 0; q < PF; q++) {
-      const int e = tid + 256 * q;
-      if (e < nt * 3 * d) tm_sm[e] = pf[q];
-    }
+    for (int q = 0; q < PF; q++) tm_sm[tid + 256 * q] = pf[q];
     vs[tid] = pv;
     __syncthreads();
     if (tb + TM_ROUND < t1) fetch(tb + TM_ROUND);     // in flight while this round is computed
-    for (int tt = 0; tt < nt; tt++) {
+    float acc[TM_ROUND];
+#pragma unroll
+    for (int tt = 0; tt < TM_ROUND; tt++) {
       const float vj = vs[tt * 16 + jl];
-      const float *rs = tm_sm + (tt * 3) * d, *ks = rs + d, *ws = ks + d;
-      float acc = 0.f;
+      const float *rs = tm_sm + tt * 3 * DP, *ks = rs + DP, *ws = ks + DP;
+      float a = 0.f;
 #pragma unroll
       for (int n = 0; n < NI; n++) {
         const int i = x + 16 * n;
-        if (i < d) {
-          const float kv = ks[i] * vj;
-          acc = fmaf(rs[i], fmaf(uu[n], kv, s[n]), acc);
-          s[n] = fmaf(ws[i], s[n], kv);
-        }
+        const float kv = ks[i] * vj;
+        a = fmaf(rs[i], fmaf(uu[n], kv, s[n]), a);
+        s[n] = fmaf(ws[i], s[n], kv);
       }
-      acc += __shfl_xor_sync(0xffffffffu, acc, 8);
-      acc += __shfl_xor_sync(0xffffffffu, acc, 4);
-      acc += __shfl_xor_sync(0xffffffffu, acc, 2);
-      acc += __shfl_xor_sync(0xffffffffu, acc, 1);
-      if (x == 0 && live) out[(size_t)(tb + tt) * H * dv + (size_t)h * dv + j] = acc;
+      acc[tt] = a;
     }
+    // The 16 threads of a column add up their shares of all 16 tokens at once: after the step with distance o a
+    // thread keeps the o sums of the half that its bit o of x names, so 15 exchanges do what 64 would, and thread x
+    // ends with token x's sum.  A token's sum is the same tree of additions whichever place of a round it has.
+#pragma unroll
+    for (int o = TM_ROUND / 2; o > 0; o >>= 1) {
+      const bool upper = x & o;
+#pragma unroll
+      for (int i = 0; i < o; i++) {
+        const float send = upper ? acc[i] : acc[i + o], keep = upper ? acc[i + o] : acc[i];
+        acc[i] = keep + __shfl_xor_sync(0xffffffffu, send, o);
+      }
+    }
+    if (x < nt && live) out[(size_t)(tb + x) * H * dv + (size_t)h * dv + j] = acc[0];
   }
   if (write_state && live) {
 #pragma unroll
@@ -196,15 +204,17 @@ extern "C" int qd_tm_scan(const float* r, const float* k, const float* v, long l
   if (n_requests <= 0) return 0;
   if (H <= 0 || H > 65535 || n_requests > 65535 || d <= 0 || d > 256 || dv <= 0) return QD_ERR_UNSUPPORTED;
   dim3 grid((dv + 15) / 16, H, n_requests);
-  const size_t smem = ((size_t)TM_ROUND * 3 * d + TM_ROUND * 16) * sizeof(float);
 #define TM_GO(NI)                                                                                                  \
+  const size_t smem = ((size_t)TM_ROUND * 3 * 16 * NI + TM_ROUND * 16) * sizeof(float);                            \
+  if (smem > 48 * 1024)                                                                                            \
+    cudaFuncSetAttribute(tm_scan_kernel<NI>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);              \
   qd_launch(tm_scan_kernel<NI>, grid, dim3(256), smem, stream, r, k, v, ld, w, u, H, d, dv, state, state_stride,   \
             s_off, cu_tokens, slots, out, write_state)
-  if (d <= 16) TM_GO(1);
-  else if (d <= 32) TM_GO(2);
-  else if (d <= 64) TM_GO(4);
-  else if (d <= 128) TM_GO(8);
-  else TM_GO(16);
+  if (d <= 16) { TM_GO(1); }
+  else if (d <= 32) { TM_GO(2); }
+  else if (d <= 64) { TM_GO(4); }
+  else if (d <= 128) { TM_GO(8); }
+  else { TM_GO(16); }
 #undef TM_GO
   return qd_last_error();
 }
