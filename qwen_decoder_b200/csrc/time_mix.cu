@@ -99,10 +99,10 @@ extern "C" int qd_tm_decay(const float* a, long long lda, int T, int R, const vo
 
 // ----------------------------------------------------------------------------------------------------------- scan
 // grid (ceil(dv / 16), H, requests), 256 threads: thread (x = tid & 15, column = tid >> 4) keeps NI elements
-// S[x + 16 n, column] of the state in registers.  r, k, w of TM_ROUND tokens arrive in shared memory per round (the
-// next round's are fetched into registers while this round is computed, so a round never waits for memory but at the
+// S[x + 16 n, column] of the state in registers.  r, k, w of TM_GROUP tokens arrive in shared memory per group (the
+// next group's are fetched into registers while this group is computed, so a group never waits for memory but at the
 // start); a token then costs NI x 4 FMAs a thread and a reduction over the 16 threads of a column.
-#define TM_ROUND 16
+#define TM_GROUP 16
 
 template <int NI>
 __global__ void __launch_bounds__(256)
@@ -112,8 +112,8 @@ tm_scan_kernel(const float* __restrict__ r_, const float* __restrict__ k_, const
                const int* __restrict__ slots, float* __restrict__ out, int write_state) {
   pdl_launch_dependents();
   pdl_wait();
-  extern __shared__ float tm_sm[];                    // [TM_ROUND][3][16 NI] r, k, w; then [TM_ROUND][16] v
-  float* vs = tm_sm + (size_t)TM_ROUND * 3 * 16 * NI;
+  extern __shared__ float tm_sm[];                    // [TM_GROUP][3][16 NI] r, k, w; then [TM_GROUP][16] v
+  float* vs = tm_sm + (size_t)TM_GROUP * 3 * 16 * NI;
   const int tid = threadIdx.x, x = tid & 15, jl = tid >> 4;
   const int h = blockIdx.y, req = blockIdx.z, j = blockIdx.x * 16 + jl;
   const bool live = j < dv;
@@ -127,13 +127,13 @@ tm_scan_kernel(const float* __restrict__ r_, const float* __restrict__ k_, const
     s[n] = (live && i < d) ? S[(size_t)i * dv + j] : 0.f;
     uu[n] = i < d ? u_[(size_t)h * d + i] : 0.f;
   }
-  // A round's operands in shared memory: [TM_ROUND][3][DP] with DP = 16 NI >= d; places past the portion's end or
+  // A group's operands in shared memory: [TM_GROUP][3][DP] with DP = 16 NI >= d; places past the portion's end or
   // past d hold r = 0, k = 0, w = 1 (and v = 0), which leave the state and the sums as they are.  Element
   // e = tid + 256 q of it is fetched by this thread, q < PF.
-  constexpr int DP = 16 * NI, PF = 3 * NI * TM_ROUND / 16;
+  constexpr int DP = 16 * NI, PF = 3 * NI * TM_GROUP / 16;
   float pf[PF], pv = 0.f;
   auto fetch = [&](int tb) {
-    const int nt = min(TM_ROUND, t1 - tb);
+    const int nt = min(TM_GROUP, t1 - tb);
 #pragma unroll
     for (int q = 0; q < PF; q++) {
       const int e = tid + 256 * q;
@@ -148,17 +148,17 @@ tm_scan_kernel(const float* __restrict__ r_, const float* __restrict__ k_, const
     pv = (tt < nt && jj < dv) ? v_[(size_t)(tb + tt) * ld + (size_t)h * dv + jj] : 0.f;
   };
   fetch(t0);
-  for (int tb = t0; tb < t1; tb += TM_ROUND) {
-    const int nt = min(TM_ROUND, t1 - tb);
-    __syncthreads();                                  // the round before is computed
+  for (int tb = t0; tb < t1; tb += TM_GROUP) {
+    const int nt = min(TM_GROUP, t1 - tb);
+    __syncthreads();                                  // the group before is computed
 #pragma unroll
     for (int q = 0; q < PF; q++) tm_sm[tid + 256 * q] = pf[q];
     vs[tid] = pv;
     __syncthreads();
-    if (tb + TM_ROUND < t1) fetch(tb + TM_ROUND);     // in flight while this round is computed
-    float acc[TM_ROUND];
+    if (tb + TM_GROUP < t1) fetch(tb + TM_GROUP);     // in flight while this group is computed
+    float acc[TM_GROUP];
 #pragma unroll
-    for (int tt = 0; tt < TM_ROUND; tt++) {
+    for (int tt = 0; tt < TM_GROUP; tt++) {
       const float vj = vs[tt * 16 + jl];
       const float *rs = tm_sm + tt * 3 * DP, *ks = rs + DP, *ws = ks + DP;
       float a = 0.f;
@@ -173,9 +173,9 @@ tm_scan_kernel(const float* __restrict__ r_, const float* __restrict__ k_, const
     }
     // The 16 threads of a column add up their shares of all 16 tokens at once: after the step with distance o a
     // thread keeps the o sums of the half that its bit o of x names, so 15 exchanges do what 64 would, and thread x
-    // ends with token x's sum.  A token's sum is the same tree of additions whichever place of a round it has.
+    // ends with token x's sum.  A token's sum is the same tree of additions whichever place of a group it has.
 #pragma unroll
-    for (int o = TM_ROUND / 2; o > 0; o >>= 1) {
+    for (int o = TM_GROUP / 2; o > 0; o >>= 1) {
       const bool upper = x & o;
 #pragma unroll
       for (int i = 0; i < o; i++) {
@@ -205,7 +205,7 @@ extern "C" int qd_tm_scan(const float* r, const float* k, const float* v, long l
   if (H <= 0 || H > 65535 || n_requests > 65535 || d <= 0 || d > 256 || dv <= 0) return QD_ERR_UNSUPPORTED;
   dim3 grid((dv + 15) / 16, H, n_requests);
 #define TM_GO(NI)                                                                                                  \
-  const size_t smem = ((size_t)TM_ROUND * 3 * 16 * NI + TM_ROUND * 16) * sizeof(float);                            \
+  const size_t smem = ((size_t)TM_GROUP * 3 * 16 * NI + TM_GROUP * 16) * sizeof(float);                            \
   if (smem > 48 * 1024)                                                                                            \
     cudaFuncSetAttribute(tm_scan_kernel<NI>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);              \
   qd_launch(tm_scan_kernel<NI>, grid, dim3(256), smem, stream, r, k, v, ld, w, u, H, d, dv, state, state_stride,   \

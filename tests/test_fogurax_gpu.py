@@ -329,3 +329,38 @@ def test_greedy_generation_through_the_engine(models):
             assert float(logits.max() - logits[tok]) <= 2 * TOL["bfloat16"] * float(logits.abs().max())
             seq.append(tok)
     all_free(e16.runner)
+
+
+def test_the_programs_take_the_folder(models, tmp_path):
+    """``bin/decoder_main`` and ``bin/trace_run`` as separate processes on a Fogurax folder: the command line's greedy
+    tokens are the statement's, and a replayed trace with four live requests in a small pool gives its logits."""
+    import os
+    import subprocess
+    import sys
+    root = os.path.join(os.path.dirname(os.path.abspath(__file__)), "..")
+    folder, cfg, w, seqs, want = models["A", "float32"]
+    prompts = [seqs[2], seqs[3]]
+    stdin = "".join(" ".join(map(str, p)) + "\n" for p in prompts) + "\n"
+    r = subprocess.run([sys.executable, os.path.join(root, "bin", "decoder_main"), folder, "8", "4096", "16", "64", "0",
+                        "--dtype", "float32", "--max-new-tokens", "5", "--num-pages", "16", "--ignore-eos"],
+                       input=stdin, capture_output=True, text=True, timeout=900)
+    assert r.returncode == 0, r.stderr
+    lines = [l for l in r.stdout.splitlines() if l.startswith("[")]
+    assert len(lines) == 2
+    for p, line in zip(prompts, lines):
+        got = [int(t) for t in line.split(")", 1)[1].split()]
+        seq = list(p)
+        for tok in got:
+            logits = pf.forward(cfg, w, seq)[-1]
+            assert float(logits.max() - logits[tok]) <= 1e-4 * float(logits.abs().max())
+            seq.append(tok)
+        assert len(got) == 5
+    tr = trace_tools.mixed(seqs, max_tokens=2 * held(seqs), seed=9)
+    out = tmp_path / "out"
+    r = subprocess.run([sys.executable, os.path.join(root, "bin", "trace_run"), "--model", folder, "--dtype", "float32",
+                        "--out", str(out), "--max-tokens", str(2 * held(seqs))], input=tr.lines(), capture_output=True,
+                       text=True, timeout=900)
+    assert r.returncode == 0, r.stderr
+    assert r.stdout.splitlines() == [f"done {s['step']}" for s in tr.steps]
+    got = trace_tools.read_outputs(tr, str(out), cfg["vocab"])
+    trace_tools.compare(tr, got, want, TOL["float32"])
