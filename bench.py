@@ -361,13 +361,13 @@ def fogurax_configs(size, layers=None):
     H, G = z["heads"]
     m, d = z["moe"], z["dim"]
     base = {"heads": H, "kv_heads": G, "dim": d, "vdim": z["vdim"], "scale": d ** -0.5}
-    conv = {"type": "attention", "mixer": dict(base, conv=4, rot={"base": 500000.0, "dims": d // 2, "scaling": {
-        "factor": 8.0, "low": 1.0, "high": 4.0, "original": 8192}})}
-    block = {"type": "attention_2", "mixer": dict(base, mask={"size": z["span"]}, rot={"base": 500000.0, "dims": d // 2, "scaling": {
-        "factor": 4.0, "original": 8192, "fast": 32.0, "slow": 1.0}})}
-    both = {"type": "parallel", "mixer": {"left": dict(base, mask={"size": z["span"]}, rot={"base": 1000000.0, "dims": d}),
+    conv = {"type": "attention", "mixer": dict(base, conv=4, rot={"base": 200000.0, "dims": d // 2, "scaling": {
+        "factor": 4.0, "low": 1.0, "high": 8.0, "original": 4096}})}
+    block = {"type": "attention_2", "mixer": dict(base, mask={"size": z["span"]}, rot={"base": 200000.0, "dims": d // 2, "scaling": {
+        "factor": 4.0, "original": 4096, "fast": 16.0, "slow": 2.0}})}
+    both = {"type": "parallel", "mixer": {"left": dict(base, mask={"size": z["span"]}, rot={"base": 10000.0, "dims": d}),
                                           "right": {"heads": z["width"] // 64, "dim": 64, "rank": z["rank"]},
-                                          "left_scale": 1.2, "right_scale": 1.1}}
+                                          "left_scale": 0.8, "right_scale": 1.25}}
     moe = {"kind": "moe", "expert": {"ff": m["ff"]}, "router": {"experts": m["experts"], "top": m["top"]},
            "shared": {"ff": m["shared"]}}
     dense = {"kind": "dense", "ff": z["ff"]}
@@ -375,7 +375,7 @@ def fogurax_configs(size, layers=None):
     if layers:                  # fewer layers of the same sizes (a capture under a profiler holds fewer weights)
         eight = eight[:max(1, layers)]
     fogurax = config_from_dict({"architecture": "Fogurax", "vocab": z["vocab"], "width": z["width"], "norm": {"eps": 1e-5},
-                                "residual_mult": 0.5, "token_side": {"dim": 256}, "layers": eight})
+                                "residual_mult": 0.7, "token_side": {"dim": 256}, "layers": eight})
     vmix = {"heads": H, "kv_heads": G, "dim": d, "vdim": z["vdim"], "scale": d ** -0.5,
             "rot": {"base": 1000000.0, "dims": d}}
     vmlp = {"kind": "moe", "expert": {"ff": m["ff"], "limit": 7.0}, "router": {"experts": m["experts"], "identity": 0,

@@ -69,7 +69,7 @@ def config(vocab, width, eps, mult, side, layers):
 # is no multiple of a page, a window shorter than a page, one recurrent head of a size that is no power of two, a
 # layer without feed-forward, several experts per token, no shared expert in one layer, every layer another kind
 FA = config(310, 96, 1e-6, 0.7, 6, [
-    (attn(6, 3, 16, 24, conv=2, rot_dims=8, base=500.0, scaling=bands(4.0, 1.0, 4.0, 64), scale=0.3), dense(40)),
+    (attn(6, 3, 16, 24, conv=2, rot_dims=8, base=500.0, scaling=bands(4.0, 0.5, 3.0, 64), scale=0.3), dense(40)),
     (par(4, 4, 24, 16, 11, 1, 40, 5, left_scale=0.8, right_scale=1.3, base=77.0), None),
     (attn2(8, 2, 8, 16, 20, rot_dims=4, scaling=ramp(4.0, 64, 16.0, 2.0), scale=0.5), moe(5, 2, 24)),
     (par(3, 1, 8, 8, 40, 3, 16, 9, left_scale=1.0, right_scale=0.6, rot_dims=6), moe(4, 4, 16, shared=24)),
@@ -81,13 +81,13 @@ FA = config(310, 96, 1e-6, 0.7, 6, [
 FB = config(515, 128, 2e-5, 1.0, 0, [
     (attn(10, 1, 12, 20, conv=0, rot_dims=4, base=300.0), moe(7, 3, 32, shared=48)),
     (attn2(2, 1, 128, 20, 1, scaling=ramp(6.0, 128, 24.0, 1.5), scale=0.1), None),
-    (par(5, 5, 72, 20, 150, 2, 64, 16, left_scale=1.2, right_scale=1.1, rot_dims=36), moe(2, 1, 64)),
-    (attn(2, 2, 128, 64, conv=1, scaling=bands(8.0, 1.0, 4.0, 32), scale=0.08), dense(72)),
+    (par(5, 5, 72, 20, 150, 3, 64, 12, left_scale=1.25, right_scale=0.9, rot_dims=36), moe(2, 1, 64)),
+    (attn(2, 2, 128, 64, conv=1, scaling=bands(6.0, 1.0, 3.0, 32), scale=0.08), dense(72)),
 ])
 CONFIGS = {"A": FA, "B": FB}
 
 
-def one_layer(mix, mlp, vocab=200, width=64, eps=1e-5, mult=0.5, side=0):
+def one_layer(mix, mlp, vocab=200, width=64, eps=3e-6, mult=0.6, side=0):
     return config(vocab, width, eps, mult, side, [(mix, mlp)])
 
 

@@ -222,12 +222,15 @@ def gated_ff(h, w, p: str) -> torch.Tensor:
     return (silu(h @ w[p + "gate"].T) * (h @ w[p + "up"].T)) @ w[p + "down"].T
 
 
-def routed_ff(h, f: dict, w, p: str, chosen_out: Optional[list] = None) -> torch.Tensor:
+def routed_ff(h, f: dict, w, p: str, chosen_out: Optional[list] = None, margins_out: Optional[list] = None) -> torch.Tensor:
     E, top = f["router"]["experts"], f["router"]["top"]
     s = torch.sigmoid(h @ w[p + "router"].T)
     pick = torch.topk(s, top, dim=-1).indices
     if chosen_out is not None:
         chosen_out.append(pick)
+    if margins_out is not None and top < E:       # how far the last chosen score lies above the first one left out
+        best = torch.topk(s, top + 1, dim=-1).values
+        margins_out.append(best[:, top - 1] - best[:, top])
     out = torch.zeros_like(h)
     for t in range(h.shape[0]):
         for e in pick[t].tolist():
@@ -241,7 +244,7 @@ MIXERS = {"attention": attention, "attention_2": attention_2, "parallel": parall
 
 
 def forward(cfg: dict, weights: Dict[str, torch.Tensor], tokens: Sequence[int], layers_out: Optional[list] = None,
-            chosen_out: Optional[list] = None) -> torch.Tensor:
+            chosen_out: Optional[list] = None, margins_out: Optional[list] = None) -> torch.Tensor:
     """Logits [T, vocab] of one sequence."""
     w = {k: v.to(F64) for k, v in weights.items() if v.is_floating_point()}
     eps, m = float(cfg["norm"]["eps"]), float(cfg.get("residual_mult", 1.0))
@@ -254,7 +257,7 @@ def forward(cfg: dict, weights: Dict[str, torch.Tensor], tokens: Sequence[int], 
         a = MIXERS[layer["type"]](h, layer["mixer"], w, p + "mix.", eps)
         f = layer.get("mlp")
         if f is not None:
-            a = a + (gated_ff(h, w, p + "mlp.") if f["kind"] == "dense" else routed_ff(h, f, w, p + "mlp.", chosen_out))
+            a = a + (gated_ff(h, w, p + "mlp.") if f["kind"] == "dense" else routed_ff(h, f, w, p + "mlp.", chosen_out, margins_out))
         x = x + m * a
         if side:
             e = w["side.embed"][tok][:, i * side:(i + 1) * side]

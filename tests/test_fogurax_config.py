@@ -69,7 +69,7 @@ def test_cache_layout_pages_and_state_rows():
     cm.check()
 
 
-@pytest.mark.parametrize("scaling", [None, fc.bands(4.0, 1.0, 4.0, 64), fc.bands(8.0, 0.5, 3.0, 2048)])
+@pytest.mark.parametrize("scaling", [None, fc.bands(4.0, 1.0, 3.0, 64), fc.bands(6.0, 0.5, 5.0, 2048)])
 def test_band_stretched_tables(scaling):
     rot = {"base": 500.0, "dims": 24}
     if scaling:
