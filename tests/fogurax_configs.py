@@ -137,3 +137,36 @@ def steady_routing(tensors) -> None:
             for j, e in enumerate(order):
                 r[e, 0] = 0.25 * (n - 1 - j) - 0.3
             tensors[name] = r
+
+
+def drawn(seed: int) -> dict:
+    """A model drawn at random: three to six layers of any kind in any order, sizes, taps, windows, blocks, constants
+    and feed-forwards drawn anew for every layer (head sizes even; some multiples of 8, some not)."""
+    import random
+    rng = random.Random(seed)
+    width = rng.choice([40, 64, 72, 96, 104])
+    layers = []
+    for _ in range(rng.randint(3, 6)):
+        kv = rng.choice([1, 2, 3])
+        heads = kv * rng.choice([1, 2, 4])
+        dim, vdim = rng.choice([8, 12, 16, 24, 32, 64]), rng.choice([8, 12, 16, 20, 40])
+        rot_dims = rng.choice([dim, dim // 2 - (dim // 2) % 2 or 2, 4])
+        base = rng.choice([50.0, 1000.0, 3e5])
+        scale = rng.choice([dim ** -0.5, 0.3, 0.5])
+        kind = rng.choice(["attention", "attention_2", "parallel"])
+        if kind == "attention":
+            sc = rng.choice([None, bands(rng.choice([2.0, 8.0]), rng.choice([0.5, 1.0]), rng.choice([2.0, 6.0]), rng.choice([16, 64]))])
+            mix = attn(heads, kv, dim, vdim, conv=rng.choice([0, 1, 2, 3, 4]), rot_dims=rot_dims, base=base, scaling=sc, scale=scale)
+        elif kind == "attention_2":
+            sc = rng.choice([None, ramp(rng.choice([2.0, 5.0]), rng.choice([16, 64]), rng.choice([4.0, 16.0]), rng.choice([0.5, 2.0]))])
+            mix = attn2(heads, kv, dim, vdim, rng.choice([1, 3, 16, 37, 64, 500]), rot_dims=rot_dims, base=base, scaling=sc, scale=scale)
+        else:
+            mix = par(heads, kv, dim, vdim, rng.choice([1, 5, 16, 50, 130, 500]), rng.choice([1, 2, 3]), rng.choice([8, 16, 24, 64]),
+                      rng.choice([2, 7, 16]), left_scale=rng.choice([0.5, 1.0, 1.4]), right_scale=rng.choice([0.4, 1.0, 1.3]),
+                      rot_dims=rot_dims, base=base, scale=scale)
+        experts = rng.choice([2, 4, 6])
+        mlp = rng.choice([None, dense(rng.choice([24, 40, 88])),
+                          moe(experts, rng.randint(1, experts), rng.choice([12, 16, 40]), shared=rng.choice([None, 24]))])
+        layers.append((mix, mlp))
+    return config(rng.choice([150, 333]), width, rng.choice([1e-6, 1e-5, 1e-4]), rng.choice([0.3, 0.7, 1.0]),
+                  rng.choice([0, 0, 3, 8]), layers)

@@ -62,12 +62,14 @@ def all_free(runner):
     assert runner.cache.free_pages() == [runner.cache.num_pages] * len(runner.cache.pools)
 
 
-def run_all_ways(folder, dtype, seqs, want, tmp_path, max_tokens=128, tail=20, sizes=(7, 2, 24, 3, 2, 16, 5, 2, 31, 2), **kw):
+def run_all_ways(folder, dtype, seqs, want, tmp_path, max_tokens=128, tail=20, sizes=(7, 2, 24, 3, 2, 16, 5, 2, 31, 2),
+                 stray=None, **kw):
+    stray = STRAY[dtype] if stray is None else stray
     runner = make_runner(folder, dtype, max_tokens, **kw)
     for k, tr in enumerate((trace_tools.whole(seqs), trace_tools.portions(seqs, sizes=sizes),
                             trace_tools.decode_tail(seqs, tail=tail))):
         got = trace_tools.run_inprocess(runner, tr, str(tmp_path / f"o{k}"))
-        trace_tools.compare(tr, got, want, TOL[dtype], stray=STRAY[dtype], stray_factor=STRAY_FACTOR)
+        trace_tools.compare(tr, got, want, TOL[dtype], stray=stray, stray_factor=STRAY_FACTOR)
     all_free(runner)
 
 
@@ -368,3 +370,28 @@ def test_the_programs_take_the_folder(models, tmp_path):
     assert r.stdout.splitlines() == [f"done {s['step']}" for s in tr.steps]
     got = trace_tools.read_outputs(tr, str(out), cfg["vocab"])
     trace_tools.compare(tr, got, want, TOL["float32"])
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+@pytest.mark.parametrize("seed", [1, 2, 3, 4, 5, 6])
+def test_models_drawn_at_random(seed, dtype, tmp_path):
+    """Layers of any kind in any order with sizes, taps, windows, blocks, constants and feed-forwards drawn anew for
+    every layer: whole, in portions, with decoded tails, and as mixed batches in a small pool with three state slots.
+    A drawn model may hold a token at which the statement itself is ill-conditioned (a recurrent head's first output is
+    one scalar times v, divided by its own size: where the scalar cancels, relative noise of 1e-7 in the weights moves
+    the statement's logits by 6e-5), so float32 too lets one row in a hundred reach four times its tolerance here."""
+    stray = max(STRAY[dtype], 0.01)
+    cfg = fc.drawn(seed)
+    folder = fc.make_folder(cfg, str(tmp_path / "m"), seed=100 + seed, std=0.13,
+                            edit=fc.steady_routing if dtype == "bfloat16" else None)
+    cfg, w = fc.read_folder(folder)
+    rng = random.Random(seed)
+    seqs = [[rng.randrange(cfg["vocab"]) for _ in range(n)] for n in (1, 2, 19, 64, 65, 141)]
+    want = expected(cfg, w, seqs)
+    run_all_ways(folder, dtype, seqs, want, tmp_path, max_tokens=192, tail=30, page_size=16 if seed % 2 else 32, stray=stray)
+    max_tokens = 2 * held(seqs)
+    runner = make_runner(folder, dtype, max_tokens, max_requests=3)
+    tr = trace_tools.mixed(seqs + seqs[::-1], max_tokens, seed=seed, max_live=3)
+    got = trace_tools.run_inprocess(runner, tr, str(tmp_path / "mixed"))
+    trace_tools.compare(tr, got, want + want[::-1], TOL[dtype], stray=stray, stray_factor=STRAY_FACTOR)
+    all_free(runner)
