@@ -395,3 +395,31 @@ def test_models_drawn_at_random(seed, dtype, tmp_path):
     got = trace_tools.run_inprocess(runner, tr, str(tmp_path / "mixed"))
     trace_tools.compare(tr, got, want + want[::-1], TOL[dtype], stray=stray, stray_factor=STRAY_FACTOR)
     all_free(runner)
+
+
+LARGER = fc.config(420, 192, 1e-5, 0.8, 16, [
+    (fc.attn(6, 2, 128, 96, conv=4, rot_dims=64, base=2e5, scaling=fc.bands(4.0, 1.0, 3.0, 256)), fc.dense(320)),
+    (fc.attn2(4, 4, 64, 128, 128, rot_dims=32, base=1e4, scaling=fc.ramp(3.0, 256, 16.0, 2.0)), fc.moe(8, 2, 96, shared=64)),
+    (fc.par(6, 3, 64, 64, 200, 3, 32, 24, left_scale=1.1, right_scale=0.9, base=5e5), fc.dense(256)),
+    (fc.attn(4, 1, 64, 40, conv=3, rot_dims=64, base=1e3), fc.moe(6, 3, 64)),
+])
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_a_larger_model_with_long_prompts(dtype, tmp_path):
+    """Heads of 128 and 64 with values of 96, 128, 64 and 40 (every form of the tensor-core kernel), groups of 1, 2, 3
+    and 4 heads, prompts of up to 700 tokens over blocks of 128 and a window of 200: several key tiles per query tile,
+    single tokens whose keys are shared among CTAs, every way of cutting, and a mixed batch in a small pool."""
+    folder = fc.make_folder(LARGER, str(tmp_path / "m"), seed=31, std=0.1,
+                            edit=fc.steady_routing if dtype == "bfloat16" else None)
+    cfg, w = fc.read_folder(folder)
+    rng = random.Random(14)
+    seqs = [[rng.randrange(cfg["vocab"]) for _ in range(n)] for n in (700, 257, 384, 129, 513)]
+    want = expected(cfg, w, seqs)
+    run_all_ways(folder, dtype, seqs, want, tmp_path, max_tokens=704, tail=40, sizes=(100, 2, 3, 64, 200, 7))
+    max_tokens = 1408
+    runner = make_runner(folder, dtype, max_tokens, max_requests=3, page_size=32)
+    tr = trace_tools.mixed(seqs, max_tokens, seed=5, max_live=3, prompt_frac=0.8, portion_sizes=(2, 9, 33, 64, 130))
+    got = trace_tools.run_inprocess(runner, tr, str(tmp_path / "mixed"))
+    trace_tools.compare(tr, got, want, TOL[dtype], stray=STRAY[dtype], stray_factor=STRAY_FACTOR)
+    all_free(runner)
